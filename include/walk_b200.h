@@ -1,0 +1,192 @@
+/*
+ * walk_b200.h -- C ABI of the B200 (sm_100a) CSR walk generators.
+ *
+ * This is the boundary a host framework binds in place of the reference's two
+ * primitives. Plain pointers and sizes only; no exceptions cross it; every entry
+ * point returns a WALK_B200_* status (0 = success) and leaves a message behind for
+ * walk_b200_last_error(). There is no CPU implementation behind any of these
+ * calls: without a CUDA device they fail with WALK_B200_ERR_CUDA.
+ *
+ * Conventions
+ *   - "device pointer" = memory of the CUDA device that is current on the calling
+ *     thread. All launches are asynchronous on `stream` (a cudaStream_t passed as
+ *     void*, NULL = the legacy default stream); outputs are valid in stream order.
+ *   - CSR arrays are int64, as in the reference: rowptr[num_nodes+1], col[num_edges].
+ *   - Walk matrix n_out is int64 [num_walks, walk_length+1], row-major; the optional
+ *     edge matrix e_out is int64 [num_walks, walk_length] (-1 where the walk stood still).
+ *   - A node without out-edges keeps the walk in place for all remaining steps.
+ *   - status_flags (optional device uint32) is OR-ed with WALK_B200_FLAG_* bits when
+ *     a kernel meets malformed input; the kernel never faults on it: it parks the
+ *     walk or clamps the index and carries on.
+ */
+#ifndef WALK_B200_H_
+#define WALK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WALK_B200_ABI_VERSION 1
+
+/* ---- return codes ---- */
+#define WALK_B200_OK 0
+#define WALK_B200_ERR_INVALID_ARG 1 /* null pointer, negative size, size overflow */
+#define WALK_B200_ERR_BAD_PQ 2      /* p or q not finite, not > 0, or acceptance threshold below 2^-16 */
+#define WALK_B200_ERR_CUDA 3        /* a CUDA runtime call failed (message has the CUDA error) */
+#define WALK_B200_ERR_CSR_INVALID 4 /* walk_b200_csr_validate / host entry points found a malformed graph */
+#define WALK_B200_ERR_UNSUPPORTED 5 /* e.g. row descriptor cannot represent this graph */
+#define WALK_B200_ERR_DEVICE_FLAGS 6 /* host entry point: the kernel raised status flags (see message) */
+
+/* ---- device status flag bits ---- */
+#define WALK_B200_FLAG_BAD_NODE 0x1u      /* a start or col value outside [0, num_nodes) */
+#define WALK_B200_FLAG_BAD_EDGE 0x2u      /* a sampled edge index outside [0, num_edges) (rand >= 1, NaN, bad rowptr) */
+#define WALK_B200_FLAG_ATTEMPT_CAP 0x4u   /* node2vec: WALK_B200_MAX_ATTEMPTS rejections in one step */
+#define WALK_B200_FLAG_BAD_ROWPTR 0x8u    /* rowptr not monotone, or rowptr[0] != 0, or rowptr[N] != num_edges */
+#define WALK_B200_FLAG_DESC_OVERFLOW 0x10u /* a row start >= 2^36 or a degree >= 2^28: no packed descriptor */
+#define WALK_B200_FLAG_UNSORTED_ROW 0x20u /* csr_validate: a row is not strictly ascending */
+#define WALK_B200_FLAG_WAIT_TIMEOUT 0x40u /* reserved */
+
+#define WALK_B200_MAX_ATTEMPTS (1u << 22)
+
+/* ---- graph description ---- */
+#define WALK_B200_CSR_SYMMETRIC 0x1u /* caller asserts (u,v) in E <=> (v,u) in E: lets node2vec search the previous
+                                        node's row instead of the candidate's; results are identical on such graphs */
+
+typedef struct walk_b200_csr {
+  const int64_t* rowptr;   /* device, [num_nodes + 1] */
+  const int64_t* col;      /* device, [num_edges]; node2vec needs each row sorted ascending */
+  int64_t num_nodes;
+  int64_t num_edges;
+  const uint64_t* rowdesc; /* device, [num_nodes], from walk_b200_rowdesc_pack, or NULL (kernels then read rowptr) */
+  uint32_t flags;          /* WALK_B200_CSR_* */
+  uint32_t reserved;
+} walk_b200_csr;
+
+/* node2vec instrumentation slots (device uint64[WALK_B200_COUNTER_COUNT], caller zeroes them) */
+enum {
+  WALK_B200_CNT_LOADS = 0,      /* 8-byte gathers issued (rowptr/rowdesc/col), all states */
+  WALK_B200_CNT_ATTEMPTS,       /* candidate draws in the rejection loop (steps >= 1, degree >= 2) */
+  WALK_B200_CNT_MEMBERSHIP,     /* membership tests actually run */
+  WALK_B200_CNT_PROBES,         /* binary-search probes of those tests */
+  WALK_B200_CNT_STEPS_DEG0,
+  WALK_B200_CNT_STEPS_DEG1,
+  WALK_B200_CNT_STEPS_SAMPLED,
+  WALK_B200_CNT_STEPS_FIRST,
+  WALK_B200_COUNTER_COUNT
+};
+
+/* ---- library ---- */
+int walk_b200_abi_version(void);
+/* Message of the last failing call on this thread ("" if none). */
+const char* walk_b200_last_error(void);
+/* Number of kernels this library has launched in this process (all threads). */
+uint64_t walk_b200_launch_count(void);
+
+/*
+ * Uniform CSR walk. Replaces RandomWalk::eval_cpu (random_walks/RandomWalk.cpp:18-62),
+ * the Metal kernel (random_walks/random_walk.metal:5-35) and its host launch
+ * RandomWalk::eval_gpu (random_walks/RandomWalk.cpp:73-108). Step l of walk w takes
+ * col[rowptr[v] + (int64)(rand[w*L+l] * (float)deg(v))], float32 product truncated
+ * toward zero, bit-for-bit as the reference. e_out and status_flags may be NULL.
+ */
+int walk_b200_uniform_walk(const walk_b200_csr* g, const int64_t* start, const float* rand,
+                           int64_t num_walks, int32_t walk_length, int64_t* n_out,
+                           int64_t* e_out, uint32_t* status_flags, void* stream);
+
+/*
+ * node2vec biased walk by rejection sampling. Replaces BiasedRandomWalk::eval_cpu
+ * (random_walks/BiasedRandomWalk.cpp:30-102, is_neighbor :20-28); the reference has
+ * no GPU version (eval_gpu throws, :150-155). Draws come from Philox4x32-10 with
+ * key = seed and counter = (walk lo32, step, attempt, walk hi32), walk =
+ * walk_index_base + row: word0>>1 picks the candidate (mod degree), word1>>1 is the
+ * accept draw r = w / 2147483647 compared against prob_0/1/2 of the reference
+ * (:52-55). Same accept/reject decisions as the reference loop fed with that stream.
+ * counters (device uint64[WALK_B200_COUNTER_COUNT]) selects the instrumented kernel
+ * when non-NULL. e_out, status_flags, counters may be NULL. walk_length 0 returns
+ * the start column only (the reference requires walk_length >= 1).
+ */
+int walk_b200_node2vec_walk(const walk_b200_csr* g, const int64_t* start, int64_t num_walks,
+                            int32_t walk_length, double p, double q, uint64_t seed,
+                            uint64_t walk_index_base, int64_t* n_out, int64_t* e_out,
+                            uint32_t* status_flags, uint64_t* counters, void* stream);
+
+/*
+ * Pack rowptr into one 8-byte descriptor per node: bits 0..35 = rowptr[v],
+ * bits 36..63 = degree. One 8-byte load then replaces the rowptr pair read of
+ * random_walks/RandomWalk.cpp:45-46 / BiasedRandomWalk.cpp:71. rowdesc is caller
+ * scratch of num_nodes * 8 bytes. Raises WALK_B200_FLAG_DESC_OVERFLOW / _BAD_ROWPTR
+ * in status_flags when the graph does not fit (then pass rowdesc = NULL to the walks).
+ */
+int walk_b200_rowdesc_pack(const int64_t* rowptr, int64_t num_nodes, int64_t num_edges,
+                           uint64_t* rowdesc, uint32_t* status_flags, void* stream);
+
+/*
+ * Full check the reference never makes (it reinterprets whatever it is given,
+ * random_walks/RandomWalk.cpp:33-38): rowptr[0]==0, monotone, rowptr[N]==num_edges,
+ * 0 <= col < N, 0 <= start < N, and (check_sorted != 0) rows strictly ascending.
+ * Findings are OR-ed into status_flags (required, device). start may be NULL.
+ */
+int walk_b200_csr_validate(const walk_b200_csr* g, const int64_t* start, int64_t num_walks,
+                           int32_t check_sorted, uint32_t* status_flags, void* stream);
+
+/*
+ * Host-side Philox4x32-10 block and the walk stream built on it, so a caller can
+ * reproduce every draw of walk_b200_node2vec_walk without a GPU.
+ */
+void walk_b200_philox4x32_10(const uint32_t counter[4], const uint32_t key[2], uint32_t out[4]);
+void walk_b200_node2vec_draw(uint64_t seed, uint64_t walk, uint32_t step, uint32_t attempt,
+                             uint32_t* candidate31, uint32_t* accept31);
+/* thresholds prob_0/1/2 (BiasedRandomWalk.cpp:52-55) and their exact integer cuts:
+ * "r < prob_k" <=> "accept31 < cuts[k]". Returns WALK_B200_ERR_BAD_PQ on bad p/q. */
+int walk_b200_node2vec_thresholds(double p, double q, double prob[3], uint32_t cuts[3]);
+
+/* Contiguous block partition of num_walks start rows over world_size ranks. */
+int walk_b200_shard_range(int64_t num_walks, int32_t world_size, int32_t rank,
+                          int64_t* begin, int64_t* end);
+
+/* ---- resident graph + host-buffer entry points ---------------------------------
+ * For callers whose arrays live in host memory. The graph is uploaded once and stays
+ * resident on the device that was current at creation; each walk call then moves
+ * only its own batch: start (+ rand) host->device and the walk matrix device->host,
+ * in slabs so that copies overlap the kernel. Host buffers should be pinned
+ * (cudaHostAlloc / cudaHostRegister) for the copies to overlap.
+ */
+typedef struct walk_b200_graph walk_b200_graph;
+
+int walk_b200_graph_create(const int64_t* h_rowptr, const int64_t* h_col, int64_t num_nodes,
+                           int64_t num_edges, uint32_t csr_flags, int32_t validate,
+                           walk_b200_graph** out);
+int walk_b200_graph_destroy(walk_b200_graph* g);
+/* Device view of a resident graph (pointers owned by the graph). */
+int walk_b200_graph_csr(const walk_b200_graph* g, walk_b200_csr* out);
+int walk_b200_graph_device_bytes(const walk_b200_graph* g, int64_t* bytes);
+
+int walk_b200_uniform_walk_host(walk_b200_graph* g, const int64_t* h_start, const float* h_rand,
+                                int64_t num_walks, int32_t walk_length, int64_t* h_n_out,
+                                int64_t* h_e_out);
+int walk_b200_node2vec_walk_host(walk_b200_graph* g, const int64_t* h_start, int64_t num_walks,
+                                 int32_t walk_length, double p, double q, uint64_t seed,
+                                 uint64_t walk_index_base, int64_t* h_n_out, int64_t* h_e_out);
+
+/* ---- L2 residency hint ----------------------------------------------------------
+ * Marks [ptr, ptr+bytes) (typically rowdesc or rowptr: the array whose accesses are
+ * skewed to hub nodes) as persisting in L2 for work launched on `stream` afterwards.
+ * Per-context, per-stream state only; walk_b200_l2_window_clear undoes it.
+ * granted_bytes (optional) receives the window actually set (0 if the device or
+ * driver configuration offers none).
+ */
+int walk_b200_l2_window_set(const void* ptr, size_t bytes, float hit_ratio, void* stream,
+                            size_t* granted_bytes);
+int walk_b200_l2_window_clear(void* stream);
+
+/* Kernel variant selection for experiments ("uniform_chunk", "n2v_block", ...); unknown keys fail. */
+int walk_b200_set_tuning(const char* key, int32_t value);
+int walk_b200_get_tuning(const char* key, int32_t* value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WALK_B200_H_ */

@@ -1,0 +1,51 @@
+// Philox4x32-10 (Salmon et al., SC'11) for host and device, and the node2vec walk
+// stream built on it: key = seed, counter = (walk lo32, step, attempt, walk hi32).
+#pragma once
+#include <cstdint>
+
+namespace walk_b200 {
+
+constexpr uint32_t kPhiloxM0 = 0xD2511F53u;
+constexpr uint32_t kPhiloxM1 = 0xCD9E8D57u;
+constexpr uint32_t kPhiloxW0 = 0x9E3779B9u;
+constexpr uint32_t kPhiloxW1 = 0xBB67AE85u;
+
+struct Philox4 {
+  uint32_t x, y, z, w;
+};
+
+__host__ __device__ __forceinline__ Philox4 philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2,
+                                                          uint32_t c3, uint32_t k0, uint32_t k1) {
+#pragma unroll
+  for (int r = 0; r < 10; r++) {
+#ifdef __CUDA_ARCH__
+    const uint32_t hi0 = __umulhi(kPhiloxM0, c0);
+    const uint32_t hi1 = __umulhi(kPhiloxM1, c2);
+    const uint32_t lo0 = kPhiloxM0 * c0;
+    const uint32_t lo1 = kPhiloxM1 * c2;
+#else
+    const uint64_t p0 = (uint64_t)kPhiloxM0 * c0;
+    const uint64_t p1 = (uint64_t)kPhiloxM1 * c2;
+    const uint32_t hi0 = (uint32_t)(p0 >> 32), lo0 = (uint32_t)p0;
+    const uint32_t hi1 = (uint32_t)(p1 >> 32), lo1 = (uint32_t)p1;
+#endif
+    const uint32_t n0 = hi1 ^ c1 ^ k0;
+    const uint32_t n2 = hi0 ^ c3 ^ k1;
+    c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+    k0 += kPhiloxW0;
+    k1 += kPhiloxW1;
+  }
+  return Philox4{c0, c1, c2, c3};
+}
+
+// Only the two words the walk consumes: candidate draw (word 0 >> 1) and accept draw
+// (word 1 >> 1), both 31-bit like glibc rand().
+__host__ __device__ __forceinline__ void node2vec_draw(uint32_t k0, uint32_t k1, uint64_t walk,
+                                                       uint32_t step, uint32_t attempt,
+                                                       uint32_t& cand31, uint32_t& acc31) {
+  const Philox4 o = philox4x32_10((uint32_t)walk, step, attempt, (uint32_t)(walk >> 32), k0, k1);
+  cand31 = o.x >> 1;
+  acc31 = o.y >> 1;
+}
+
+}  // namespace walk_b200

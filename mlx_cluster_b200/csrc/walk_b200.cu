@@ -1,0 +1,574 @@
+// Host launch/stream layer and C ABI of the B200 walk generators (see include/walk_b200.h).
+//
+// Everything a framework binds lives behind extern "C": argument checks, threshold
+// arithmetic, kernel selection, launches on the caller's stream, the resident-graph
+// handle and the slab pipeline for host buffers. No torch types, no exceptions.
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <new>
+#include <string>
+
+#include "../../include/walk_b200.h"
+#include "walk_kernels.cuh"
+
+namespace {
+
+using namespace walk_b200;
+
+thread_local std::string g_last_error;
+std::atomic<uint64_t> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+#define CUDA_TRY(expr)                                                                      \
+  do {                                                                                      \
+    cudaError_t err__ = (expr);                                                             \
+    if (err__ != cudaSuccess)                                                               \
+      return fail(WALK_B200_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(err__));   \
+  } while (0)
+
+int check_launch(const char* what) {
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess)
+    return fail(WALK_B200_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(err));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return WALK_B200_OK;
+}
+
+// ---- tuning knobs (experiments; defaults are the measured best) ------------------
+struct Tuning {
+  std::atomic<int32_t> uniform_variant{0};  // 0 auto, 1 direct, 2 staged S=8, 3 staged S=16, 4 staged S=4
+  std::atomic<int32_t> n2v_idx{0};          // 0 auto (32-bit indices when they fit), 1 force 64-bit
+  std::atomic<int32_t> host_slab_mb{256};   // walk-matrix bytes per pipeline slab of the host entry points
+  std::atomic<int32_t> use_rowdesc{1};      // host entry points: build and use the packed row descriptor
+} g_tuning;
+
+std::atomic<int32_t>* tuning_slot(const char* key) {
+  if (!key) return nullptr;
+  if (!strcmp(key, "uniform_variant")) return &g_tuning.uniform_variant;
+  if (!strcmp(key, "n2v_idx")) return &g_tuning.n2v_idx;
+  if (!strcmp(key, "host_slab_mb")) return &g_tuning.host_slab_mb;
+  if (!strcmp(key, "use_rowdesc")) return &g_tuning.use_rowdesc;
+  return nullptr;
+}
+
+int check_csr(const walk_b200_csr* g) {
+  if (!g) return fail(WALK_B200_ERR_INVALID_ARG, "csr descriptor is NULL");
+  if (g->num_nodes < 0 || g->num_edges < 0)
+    return fail(WALK_B200_ERR_INVALID_ARG, "negative graph size (num_nodes=%lld, num_edges=%lld)",
+                (long long)g->num_nodes, (long long)g->num_edges);
+  if (!g->rowptr) return fail(WALK_B200_ERR_INVALID_ARG, "rowptr is NULL");
+  if (g->num_edges > 0 && !g->col) return fail(WALK_B200_ERR_INVALID_ARG, "col is NULL");
+  return WALK_B200_OK;
+}
+
+int check_walk_sizes(int64_t num_walks, int32_t walk_length, const void* start, const void* n_out) {
+  if (num_walks < 0) return fail(WALK_B200_ERR_INVALID_ARG, "num_walks is negative");
+  if (walk_length < 0) return fail(WALK_B200_ERR_INVALID_ARG, "walk_length is negative");
+  if (num_walks > 0 && (!start || !n_out))
+    return fail(WALK_B200_ERR_INVALID_ARG, "start or n_out is NULL");
+  // row pitch * rows must stay inside int64 element indices
+  if (num_walks > 0 && (int64_t)(walk_length + 1ll) > (INT64_MAX / 8) / num_walks)
+    return fail(WALK_B200_ERR_INVALID_ARG, "num_walks * (walk_length + 1) overflows");
+  return WALK_B200_OK;
+}
+
+int64_t blocks_for(int64_t n) { return (n + kBlock - 1) / kBlock; }
+
+// ---- thresholds -------------------------------------------------------------------
+constexpr double kRandMax = 2147483647.0;
+
+uint32_t accept_cut(double prob) {
+  // smallest 31-bit draw w with (double)w / RAND_MAX >= prob; 2^31 if there is none
+  uint64_t lo = 0, hi = (uint64_t)2147483647 + 1;
+  while (lo < hi) {
+    const uint64_t mid = lo + (hi - lo) / 2;
+    if ((double)mid / kRandMax >= prob) hi = mid; else lo = mid + 1;
+  }
+  return (uint32_t)lo;
+}
+
+int thresholds(double p, double q, double prob[3], uint32_t cuts[3]) {
+  if (!(p > 0.0) || !(q > 0.0) || !std::isfinite(p) || !std::isfinite(q))
+    return fail(WALK_B200_ERR_BAD_PQ, "p and q must be finite and > 0 (got p=%g, q=%g)", p, q);
+  const double max_prob = std::fmax(std::fmax(1. / p, 1.), 1. / q);
+  prob[0] = 1. / p / max_prob;
+  prob[1] = 1. / max_prob;
+  prob[2] = 1. / q / max_prob;
+  for (int k = 0; k < 3; k++) {
+    if (!(prob[k] >= 1.0 / 65536.0))
+      return fail(WALK_B200_ERR_BAD_PQ,
+                  "p=%g, q=%g give an acceptance threshold of %g (< 2^-16): the rejection loop would not end",
+                  p, q, prob[k]);
+    cuts[k] = accept_cut(prob[k]);
+  }
+  return WALK_B200_OK;
+}
+
+// ---- launches ---------------------------------------------------------------------
+template <bool USE_DESC, bool HAS_EOUT>
+int launch_uniform_t(const UniformParams& P, cudaStream_t s) {
+  int variant = g_tuning.uniform_variant.load();
+  if (variant == 0) variant = P.walk_length >= 4 ? 2 : 1;
+  const int64_t n = P.num_walks;
+  switch (variant) {
+    case 1:
+      uniform_walk_direct_kernel<USE_DESC, HAS_EOUT><<<(unsigned)blocks_for(n), kBlock, 0, s>>>(P);
+      return check_launch("uniform_walk_direct_kernel");
+    case 3:
+      uniform_walk_staged_kernel<16, USE_DESC, HAS_EOUT><<<(unsigned)blocks_for(n), kBlock, 0, s>>>(P);
+      return check_launch("uniform_walk_staged_kernel<16>");
+    case 4:
+      uniform_walk_staged_kernel<4, USE_DESC, HAS_EOUT><<<(unsigned)blocks_for(n), kBlock, 0, s>>>(P);
+      return check_launch("uniform_walk_staged_kernel<4>");
+    case 2:
+    default:
+      uniform_walk_staged_kernel<8, USE_DESC, HAS_EOUT><<<(unsigned)blocks_for(n), kBlock, 0, s>>>(P);
+      return check_launch("uniform_walk_staged_kernel<8>");
+  }
+}
+
+int launch_uniform(const UniformParams& P, cudaStream_t s) {
+  const bool d = P.desc != nullptr, e = P.e_out != nullptr;
+  if (d) return e ? launch_uniform_t<true, true>(P, s) : launch_uniform_t<true, false>(P, s);
+  return e ? launch_uniform_t<false, true>(P, s) : launch_uniform_t<false, false>(P, s);
+}
+
+template <typename idx_t, bool SYM, bool USE_DESC>
+int launch_n2v_t(const Node2vecParams& P, cudaStream_t s) {
+  const unsigned grid = (unsigned)blocks_for(P.num_walks);
+  const bool e = P.e_out != nullptr, c = P.counters != nullptr;
+  if (c) {
+    if (e) node2vec_walk_kernel<idx_t, SYM, USE_DESC, true, true><<<grid, kBlock, 0, s>>>(P);
+    else node2vec_walk_kernel<idx_t, SYM, USE_DESC, false, true><<<grid, kBlock, 0, s>>>(P);
+  } else {
+    if (e) node2vec_walk_kernel<idx_t, SYM, USE_DESC, true, false><<<grid, kBlock, 0, s>>>(P);
+    else node2vec_walk_kernel<idx_t, SYM, USE_DESC, false, false><<<grid, kBlock, 0, s>>>(P);
+  }
+  return check_launch("node2vec_walk_kernel");
+}
+
+template <typename idx_t>
+int launch_n2v_i(const Node2vecParams& P, bool sym, cudaStream_t s) {
+  const bool d = P.desc != nullptr;
+  if (sym) return d ? launch_n2v_t<idx_t, true, true>(P, s) : launch_n2v_t<idx_t, true, false>(P, s);
+  return d ? launch_n2v_t<idx_t, false, true>(P, s) : launch_n2v_t<idx_t, false, false>(P, s);
+}
+
+int launch_n2v(const Node2vecParams& P, bool sym, cudaStream_t s) {
+  const bool fits32 = P.num_nodes <= 0x7fffffffll && P.num_edges <= 0xffffffffll;
+  if (fits32 && g_tuning.n2v_idx.load() != 1) return launch_n2v_i<uint32_t>(P, sym, s);
+  return launch_n2v_i<int64_t>(P, sym, s);
+}
+
+int grid_for_streaming(int64_t n) {
+  int64_t b = blocks_for(n);
+  const int64_t cap = 148 * 16;  // 16 resident blocks' worth per SM of a 148-SM part
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return (int)b;
+}
+
+}  // namespace
+
+// ======================================================================================
+// C ABI
+// ======================================================================================
+extern "C" {
+
+int walk_b200_abi_version(void) { return WALK_B200_ABI_VERSION; }
+
+const char* walk_b200_last_error(void) { return g_last_error.c_str(); }
+
+uint64_t walk_b200_launch_count(void) { return g_launches.load(); }
+
+int walk_b200_set_tuning(const char* key, int32_t value) {
+  auto* slot = tuning_slot(key);
+  if (!slot) return fail(WALK_B200_ERR_INVALID_ARG, "unknown tuning key '%s'", key ? key : "(null)");
+  slot->store(value);
+  return WALK_B200_OK;
+}
+
+int walk_b200_get_tuning(const char* key, int32_t* value) {
+  auto* slot = tuning_slot(key);
+  if (!slot || !value) return fail(WALK_B200_ERR_INVALID_ARG, "unknown tuning key '%s'", key ? key : "(null)");
+  *value = slot->load();
+  return WALK_B200_OK;
+}
+
+void walk_b200_philox4x32_10(const uint32_t counter[4], const uint32_t key[2], uint32_t out[4]) {
+  const Philox4 o = philox4x32_10(counter[0], counter[1], counter[2], counter[3], key[0], key[1]);
+  out[0] = o.x; out[1] = o.y; out[2] = o.z; out[3] = o.w;
+}
+
+void walk_b200_node2vec_draw(uint64_t seed, uint64_t walk, uint32_t step, uint32_t attempt,
+                             uint32_t* candidate31, uint32_t* accept31) {
+  uint32_t c, a;
+  node2vec_draw((uint32_t)seed, (uint32_t)(seed >> 32), walk, step, attempt, c, a);
+  if (candidate31) *candidate31 = c;
+  if (accept31) *accept31 = a;
+}
+
+int walk_b200_node2vec_thresholds(double p, double q, double prob[3], uint32_t cuts[3]) {
+  double pr[3];
+  uint32_t cu[3];
+  int rc = thresholds(p, q, pr, cu);
+  if (rc) return rc;
+  for (int k = 0; k < 3; k++) {
+    if (prob) prob[k] = pr[k];
+    if (cuts) cuts[k] = cu[k];
+  }
+  return WALK_B200_OK;
+}
+
+int walk_b200_shard_range(int64_t num_walks, int32_t world_size, int32_t rank, int64_t* begin, int64_t* end) {
+  if (num_walks < 0 || world_size < 1 || rank < 0 || rank >= world_size || !begin || !end)
+    return fail(WALK_B200_ERR_INVALID_ARG, "bad shard request (num_walks=%lld, world_size=%d, rank=%d)",
+                (long long)num_walks, world_size, rank);
+  const int64_t per = (num_walks + world_size - 1) / world_size;
+  int64_t b = per * rank, e = b + per;
+  if (b > num_walks) b = num_walks;
+  if (e > num_walks) e = num_walks;
+  *begin = b;
+  *end = e;
+  return WALK_B200_OK;
+}
+
+int walk_b200_uniform_walk(const walk_b200_csr* g, const int64_t* start, const float* rand,
+                           int64_t num_walks, int32_t walk_length, int64_t* n_out, int64_t* e_out,
+                           uint32_t* status_flags, void* stream) {
+  if (int rc = check_csr(g)) return rc;
+  if (int rc = check_walk_sizes(num_walks, walk_length, start, n_out)) return rc;
+  if (num_walks > 0 && walk_length > 0 && !rand) return fail(WALK_B200_ERR_INVALID_ARG, "rand is NULL");
+  if (num_walks == 0) return WALK_B200_OK;
+  UniformParams P{};
+  P.rowptr = g->rowptr; P.col = g->col; P.desc = g->rowdesc;
+  P.num_nodes = g->num_nodes; P.num_edges = g->num_edges;
+  P.start = start; P.rand = rand; P.num_walks = num_walks; P.walk_length = walk_length;
+  P.n_out = n_out; P.e_out = walk_length > 0 ? e_out : nullptr; P.flags = status_flags;
+  return launch_uniform(P, (cudaStream_t)stream);
+}
+
+int walk_b200_node2vec_walk(const walk_b200_csr* g, const int64_t* start, int64_t num_walks,
+                            int32_t walk_length, double p, double q, uint64_t seed,
+                            uint64_t walk_index_base, int64_t* n_out, int64_t* e_out,
+                            uint32_t* status_flags, uint64_t* counters, void* stream) {
+  if (int rc = check_csr(g)) return rc;
+  if (int rc = check_walk_sizes(num_walks, walk_length, start, n_out)) return rc;
+  double prob[3];
+  uint32_t cuts[3];
+  if (int rc = thresholds(p, q, prob, cuts)) return rc;
+  if (num_walks == 0) return WALK_B200_OK;
+  Node2vecParams P{};
+  P.rowptr = g->rowptr; P.col = g->col; P.desc = g->rowdesc;
+  P.num_nodes = g->num_nodes; P.num_edges = g->num_edges;
+  P.start = start; P.num_walks = num_walks; P.walk_length = walk_length;
+  P.cut0 = cuts[0]; P.cut1 = cuts[1]; P.cut2 = cuts[2];
+  P.key0 = (uint32_t)seed; P.key1 = (uint32_t)(seed >> 32);
+  P.walk_index_base = walk_index_base;
+  P.max_attempts = WALK_B200_MAX_ATTEMPTS;
+  P.n_out = n_out; P.e_out = walk_length > 0 ? e_out : nullptr;
+  P.flags = status_flags; P.counters = (unsigned long long*)counters;
+  return launch_n2v(P, (g->flags & WALK_B200_CSR_SYMMETRIC) != 0, (cudaStream_t)stream);
+}
+
+int walk_b200_rowdesc_pack(const int64_t* rowptr, int64_t num_nodes, int64_t num_edges,
+                           uint64_t* rowdesc, uint32_t* status_flags, void* stream) {
+  if (num_nodes < 0 || num_edges < 0) return fail(WALK_B200_ERR_INVALID_ARG, "negative graph size");
+  if (!rowptr || (num_nodes > 0 && !rowdesc)) return fail(WALK_B200_ERR_INVALID_ARG, "rowptr or rowdesc is NULL");
+  if (num_nodes == 0) return WALK_B200_OK;
+  rowdesc_pack_kernel<<<grid_for_streaming(num_nodes), kBlock, 0, (cudaStream_t)stream>>>(
+      rowptr, num_nodes, num_edges, rowdesc, status_flags);
+  return check_launch("rowdesc_pack_kernel");
+}
+
+int walk_b200_csr_validate(const walk_b200_csr* g, const int64_t* start, int64_t num_walks,
+                           int32_t check_sorted, uint32_t* status_flags, void* stream) {
+  if (int rc = check_csr(g)) return rc;
+  if (!status_flags) return fail(WALK_B200_ERR_INVALID_ARG, "status_flags is required");
+  if (num_walks < 0) return fail(WALK_B200_ERR_INVALID_ARG, "num_walks is negative");
+  int64_t work = g->num_nodes;
+  if (g->num_edges > work) work = g->num_edges;
+  if (num_walks > work) work = num_walks;
+  csr_validate_kernel<<<grid_for_streaming(work), kBlock, 0, (cudaStream_t)stream>>>(
+      g->rowptr, g->col, g->num_nodes, g->num_edges, start, start ? num_walks : 0, check_sorted, status_flags);
+  return check_launch("csr_validate_kernel");
+}
+
+// ---- L2 residency hint -------------------------------------------------------------
+int walk_b200_l2_window_set(const void* ptr, size_t bytes, float hit_ratio, void* stream, size_t* granted_bytes) {
+  if (granted_bytes) *granted_bytes = 0;
+  if (!ptr || bytes == 0) return fail(WALK_B200_ERR_INVALID_ARG, "empty L2 window");
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  int max_window = 0, max_persist = 0;
+  CUDA_TRY(cudaDeviceGetAttribute(&max_window, cudaDevAttrMaxAccessPolicyWindowSize, dev));
+  CUDA_TRY(cudaDeviceGetAttribute(&max_persist, cudaDevAttrMaxPersistingL2CacheSize, dev));
+  if (max_window <= 0 || max_persist <= 0) return WALK_B200_OK;  // nothing on offer: not an error
+  CUDA_TRY(cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, (size_t)max_persist));
+  size_t win = bytes < (size_t)max_window ? bytes : (size_t)max_window;
+  cudaStreamAttrValue attr;
+  memset(&attr, 0, sizeof(attr));
+  attr.accessPolicyWindow.base_ptr = const_cast<void*>(ptr);
+  attr.accessPolicyWindow.num_bytes = win;
+  float ratio = hit_ratio;
+  if (!(ratio > 0.f) || ratio > 1.f) {
+    // fill the carve-out once: hit the fraction of the window that fits
+    ratio = win <= (size_t)max_persist ? 1.f : (float)max_persist / (float)win;
+  }
+  attr.accessPolicyWindow.hitRatio = ratio;
+  attr.accessPolicyWindow.hitProp = cudaAccessPropertyPersisting;
+  attr.accessPolicyWindow.missProp = cudaAccessPropertyStreaming;
+  CUDA_TRY(cudaStreamSetAttribute((cudaStream_t)stream, cudaStreamAttributeAccessPolicyWindow, &attr));
+  if (granted_bytes) *granted_bytes = win;
+  return WALK_B200_OK;
+}
+
+int walk_b200_l2_window_clear(void* stream) {
+  cudaStreamAttrValue attr;
+  memset(&attr, 0, sizeof(attr));
+  attr.accessPolicyWindow.num_bytes = 0;
+  attr.accessPolicyWindow.hitProp = cudaAccessPropertyNormal;
+  attr.accessPolicyWindow.missProp = cudaAccessPropertyNormal;
+  CUDA_TRY(cudaStreamSetAttribute((cudaStream_t)stream, cudaStreamAttributeAccessPolicyWindow, &attr));
+  CUDA_TRY(cudaCtxResetPersistingL2Cache());
+  return WALK_B200_OK;
+}
+
+}  // extern "C"
+
+// ======================================================================================
+// Resident graph + host-buffer entry points
+// ======================================================================================
+struct walk_b200_graph {
+  int device = 0;
+  int64_t num_nodes = 0, num_edges = 0;
+  uint32_t csr_flags = 0;
+  int64_t* d_rowptr = nullptr;
+  int64_t* d_col = nullptr;
+  uint64_t* d_desc = nullptr;
+  uint32_t* d_flags = nullptr;
+  static constexpr int kLanes = 3;  // slabs in flight: copy-in, kernel, copy-out
+  cudaStream_t streams[kLanes] = {};
+  int64_t* d_start[kLanes] = {};
+  float* d_rand[kLanes] = {};
+  int64_t* d_out[kLanes] = {};
+  int64_t* d_eout[kLanes] = {};
+  size_t cap_start = 0, cap_rand = 0, cap_out = 0, cap_eout = 0;  // bytes per lane
+  std::mutex mu;
+};
+
+namespace {
+
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = false;
+  explicit DeviceGuard(int dev) {
+    if (cudaGetDevice(&prev) == cudaSuccess && cudaSetDevice(dev) == cudaSuccess) ok = true;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+template <typename T>
+int grow(T** bufs, size_t* cap, size_t need) {
+  if (need <= *cap) return WALK_B200_OK;
+  for (int k = 0; k < walk_b200_graph::kLanes; k++) {
+    if (bufs[k]) cudaFree(bufs[k]);
+    bufs[k] = nullptr;
+  }
+  *cap = 0;
+  for (int k = 0; k < walk_b200_graph::kLanes; k++) CUDA_TRY(cudaMalloc((void**)&bufs[k], need));
+  *cap = need;
+  return WALK_B200_OK;
+}
+
+int flags_to_status(uint32_t f) {
+  if (!f) return WALK_B200_OK;
+  return fail(WALK_B200_ERR_DEVICE_FLAGS,
+              "kernel raised status flags 0x%x:%s%s%s%s%s%s", f,
+              (f & WALK_B200_FLAG_BAD_NODE) ? " node id out of range;" : "",
+              (f & WALK_B200_FLAG_BAD_EDGE) ? " edge index out of range (rand outside [0,1)?);" : "",
+              (f & WALK_B200_FLAG_ATTEMPT_CAP) ? " rejection attempt cap hit;" : "",
+              (f & WALK_B200_FLAG_BAD_ROWPTR) ? " rowptr malformed;" : "",
+              (f & WALK_B200_FLAG_DESC_OVERFLOW) ? " row descriptor overflow;" : "",
+              (f & WALK_B200_FLAG_UNSORTED_ROW) ? " row not strictly ascending;" : "");
+}
+
+// Runs one walk over host buffers in slabs: H2D(start[, rand]) -> kernel -> D2H(walks)
+// per slab, slabs round-robin over kLanes streams so copies in both directions overlap
+// the kernels of neighbouring slabs.
+int run_host_walk(walk_b200_graph* g, bool biased, const int64_t* h_start, const float* h_rand,
+                  int64_t n, int32_t L, double p, double q, uint64_t seed, uint64_t base,
+                  int64_t* h_n_out, int64_t* h_e_out) {
+  if (!g) return fail(WALK_B200_ERR_INVALID_ARG, "graph handle is NULL");
+  if (int rc = check_walk_sizes(n, L, h_start, h_n_out)) return rc;
+  if (!biased && n > 0 && L > 0 && !h_rand) return fail(WALK_B200_ERR_INVALID_ARG, "rand is NULL");
+  double prob[3];
+  uint32_t cuts[3];
+  if (biased) if (int rc = thresholds(p, q, prob, cuts)) return rc;
+  if (n == 0) return WALK_B200_OK;
+
+  std::lock_guard<std::mutex> lock(g->mu);
+  DeviceGuard dg(g->device);
+  if (!dg.ok) return fail(WALK_B200_ERR_CUDA, "cannot select device %d", g->device);
+
+  const size_t row_bytes = (size_t)(L + 1) * 8;
+  int64_t slab_rows = (int64_t)(((size_t)g_tuning.host_slab_mb.load() << 20) / row_bytes);
+  if (slab_rows < 1024) slab_rows = 1024;
+  slab_rows = (slab_rows + 255) / 256 * 256;
+  if (slab_rows > n) slab_rows = n;
+  if (int rc = grow(g->d_start, &g->cap_start, (size_t)slab_rows * 8)) return rc;
+  if (int rc = grow(g->d_out, &g->cap_out, (size_t)slab_rows * row_bytes)) return rc;
+  if (!biased && L > 0) if (int rc = grow(g->d_rand, &g->cap_rand, (size_t)slab_rows * L * 4)) return rc;
+  if (h_e_out && L > 0) if (int rc = grow(g->d_eout, &g->cap_eout, (size_t)slab_rows * L * 8)) return rc;
+
+  CUDA_TRY(cudaMemsetAsync(g->d_flags, 0, sizeof(uint32_t), g->streams[0]));
+  CUDA_TRY(cudaStreamSynchronize(g->streams[0]));
+
+  walk_b200_csr csr{};
+  csr.rowptr = g->d_rowptr; csr.col = g->d_col; csr.num_nodes = g->num_nodes; csr.num_edges = g->num_edges;
+  csr.rowdesc = g->d_desc; csr.flags = g->csr_flags;
+
+  int lane = 0;
+  for (int64_t r0 = 0; r0 < n; r0 += slab_rows, lane = (lane + 1) % walk_b200_graph::kLanes) {
+    const int64_t rows = (n - r0 < slab_rows) ? n - r0 : slab_rows;
+    cudaStream_t s = g->streams[lane];
+    CUDA_TRY(cudaMemcpyAsync(g->d_start[lane], h_start + r0, (size_t)rows * 8, cudaMemcpyHostToDevice, s));
+    int64_t* d_e = (h_e_out && L > 0) ? g->d_eout[lane] : nullptr;
+    int rc;
+    if (biased) {
+      rc = walk_b200_node2vec_walk(&csr, g->d_start[lane], rows, L, p, q, seed, base + (uint64_t)r0,
+                                   g->d_out[lane], d_e, g->d_flags, nullptr, s);
+    } else {
+      if (L > 0)
+        CUDA_TRY(cudaMemcpyAsync(g->d_rand[lane], h_rand + r0 * L, (size_t)rows * L * 4, cudaMemcpyHostToDevice, s));
+      rc = walk_b200_uniform_walk(&csr, g->d_start[lane], g->d_rand[lane], rows, L, g->d_out[lane], d_e,
+                                  g->d_flags, s);
+    }
+    if (rc) return rc;
+    CUDA_TRY(cudaMemcpyAsync(h_n_out + r0 * (L + 1), g->d_out[lane], (size_t)rows * row_bytes, cudaMemcpyDeviceToHost, s));
+    if (d_e) CUDA_TRY(cudaMemcpyAsync(h_e_out + r0 * L, d_e, (size_t)rows * L * 8, cudaMemcpyDeviceToHost, s));
+  }
+  for (int k = 0; k < walk_b200_graph::kLanes; k++) CUDA_TRY(cudaStreamSynchronize(g->streams[k]));
+  uint32_t f = 0;
+  CUDA_TRY(cudaMemcpy(&f, g->d_flags, sizeof(f), cudaMemcpyDeviceToHost));
+  return flags_to_status(f);
+}
+
+}  // namespace
+
+extern "C" {
+
+int walk_b200_graph_create(const int64_t* h_rowptr, const int64_t* h_col, int64_t num_nodes,
+                           int64_t num_edges, uint32_t csr_flags, int32_t validate, walk_b200_graph** out) {
+  if (!out) return fail(WALK_B200_ERR_INVALID_ARG, "out is NULL");
+  *out = nullptr;
+  if (num_nodes < 0 || num_edges < 0 || !h_rowptr || (num_edges > 0 && !h_col))
+    return fail(WALK_B200_ERR_INVALID_ARG, "bad graph arguments");
+  walk_b200_graph* g = new (std::nothrow) walk_b200_graph();
+  if (!g) return fail(WALK_B200_ERR_INVALID_ARG, "out of host memory");
+  auto bail = [&](int rc) { std::string keep = g_last_error; walk_b200_graph_destroy(g); g_last_error = keep; return rc; };
+#define G_TRY(expr)                                                                                   \
+  do {                                                                                                \
+    cudaError_t err__ = (expr);                                                                       \
+    if (err__ != cudaSuccess)                                                                         \
+      return bail(fail(WALK_B200_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(err__)));       \
+  } while (0)
+  G_TRY(cudaGetDevice(&g->device));
+  g->num_nodes = num_nodes; g->num_edges = num_edges; g->csr_flags = csr_flags;
+  for (int k = 0; k < walk_b200_graph::kLanes; k++) G_TRY(cudaStreamCreateWithFlags(&g->streams[k], cudaStreamNonBlocking));
+  G_TRY(cudaMalloc((void**)&g->d_rowptr, (size_t)(num_nodes + 1) * 8));
+  G_TRY(cudaMalloc((void**)&g->d_col, (size_t)(num_edges > 0 ? num_edges : 1) * 8));
+  G_TRY(cudaMalloc((void**)&g->d_flags, 256));
+  cudaStream_t s = g->streams[0];
+  G_TRY(cudaMemsetAsync(g->d_flags, 0, 256, s));
+  G_TRY(cudaMemcpyAsync(g->d_rowptr, h_rowptr, (size_t)(num_nodes + 1) * 8, cudaMemcpyHostToDevice, s));
+  if (num_edges > 0) G_TRY(cudaMemcpyAsync(g->d_col, h_col, (size_t)num_edges * 8, cudaMemcpyHostToDevice, s));
+  uint32_t f = 0;
+  if (validate) {
+    walk_b200_csr csr{};
+    csr.rowptr = g->d_rowptr; csr.col = g->d_col; csr.num_nodes = num_nodes; csr.num_edges = num_edges;
+    if (int rc = walk_b200_csr_validate(&csr, nullptr, 0, 1, g->d_flags, s)) return bail(rc);
+    G_TRY(cudaMemcpyAsync(&f, g->d_flags, 4, cudaMemcpyDeviceToHost, s));
+    G_TRY(cudaStreamSynchronize(s));
+    if (f) { flags_to_status(f); return bail(fail(WALK_B200_ERR_CSR_INVALID, "graph failed validation: %s", std::string(g_last_error).c_str())); }
+  }
+  if (g_tuning.use_rowdesc.load() && num_nodes > 0) {
+    G_TRY(cudaMalloc((void**)&g->d_desc, (size_t)num_nodes * 8));
+    if (int rc = walk_b200_rowdesc_pack(g->d_rowptr, num_nodes, num_edges, g->d_desc, g->d_flags, s)) return bail(rc);
+    G_TRY(cudaMemcpyAsync(&f, g->d_flags, 4, cudaMemcpyDeviceToHost, s));
+    G_TRY(cudaStreamSynchronize(s));
+    if (f & WALK_B200_FLAG_BAD_ROWPTR) { return bail(fail(WALK_B200_ERR_CSR_INVALID, "rowptr is not a monotone prefix array ending at num_edges")); }
+    if (f & WALK_B200_FLAG_DESC_OVERFLOW) {  // graph too large for the packed form: walk from rowptr
+      cudaFree(g->d_desc);
+      g->d_desc = nullptr;
+    }
+  }
+  G_TRY(cudaStreamSynchronize(s));
+#undef G_TRY
+  *out = g;
+  return WALK_B200_OK;
+}
+
+int walk_b200_graph_destroy(walk_b200_graph* g) {
+  if (!g) return WALK_B200_OK;
+  {
+    DeviceGuard dg(g->device);
+    for (int k = 0; k < walk_b200_graph::kLanes; k++) {
+      if (g->streams[k]) { cudaStreamSynchronize(g->streams[k]); cudaStreamDestroy(g->streams[k]); }
+      if (g->d_start[k]) cudaFree(g->d_start[k]);
+      if (g->d_rand[k]) cudaFree(g->d_rand[k]);
+      if (g->d_out[k]) cudaFree(g->d_out[k]);
+      if (g->d_eout[k]) cudaFree(g->d_eout[k]);
+    }
+    if (g->d_rowptr) cudaFree(g->d_rowptr);
+    if (g->d_col) cudaFree(g->d_col);
+    if (g->d_desc) cudaFree(g->d_desc);
+    if (g->d_flags) cudaFree(g->d_flags);
+  }
+  delete g;
+  return WALK_B200_OK;
+}
+
+int walk_b200_graph_csr(const walk_b200_graph* g, walk_b200_csr* out) {
+  if (!g || !out) return fail(WALK_B200_ERR_INVALID_ARG, "graph or out is NULL");
+  memset(out, 0, sizeof(*out));
+  out->rowptr = g->d_rowptr; out->col = g->d_col; out->num_nodes = g->num_nodes; out->num_edges = g->num_edges;
+  out->rowdesc = g->d_desc; out->flags = g->csr_flags;
+  return WALK_B200_OK;
+}
+
+int walk_b200_graph_device_bytes(const walk_b200_graph* g, int64_t* bytes) {
+  if (!g || !bytes) return fail(WALK_B200_ERR_INVALID_ARG, "graph or bytes is NULL");
+  *bytes = (g->num_nodes + 1) * 8 + g->num_edges * 8 + (g->d_desc ? g->num_nodes * 8 : 0);
+  return WALK_B200_OK;
+}
+
+int walk_b200_uniform_walk_host(walk_b200_graph* g, const int64_t* h_start, const float* h_rand,
+                                int64_t num_walks, int32_t walk_length, int64_t* h_n_out, int64_t* h_e_out) {
+  return run_host_walk(g, false, h_start, h_rand, num_walks, walk_length, 1.0, 1.0, 0, 0, h_n_out, h_e_out);
+}
+
+int walk_b200_node2vec_walk_host(walk_b200_graph* g, const int64_t* h_start, int64_t num_walks,
+                                 int32_t walk_length, double p, double q, uint64_t seed,
+                                 uint64_t walk_index_base, int64_t* h_n_out, int64_t* h_e_out) {
+  return run_host_walk(g, true, h_start, nullptr, num_walks, walk_length, p, q, seed, walk_index_base, h_n_out, h_e_out);
+}
+
+}  // extern "C"

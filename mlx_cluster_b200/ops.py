@@ -1,0 +1,346 @@
+"""Host-side mirror of the reference's operator interface for the walk path.
+
+``random_walk`` and ``rejection_sampling`` keep the names, positional order and
+keyword-only ``stream`` of the reference's Python API (``bindings.cpp:12-21`` and
+``bindings.cpp:35-45``; re-exported at ``mlx_cluster/__init__.py:3-4``) and return the
+node sequence ``[n_start, walk_length + 1]`` as the reference's factories do
+(``random_walks/RandomWalk.cpp:138-148``, ``random_walks/BiasedRandomWalk.cpp:183-193``).
+Arrays are ``torch`` tensors: CUDA tensors run in place on their device, stream-ordered
+and asynchronous like any torch CUDA op; CPU tensors / numpy arrays go through the
+resident-graph host entry points (graph uploaded once, per-call batch copied in slabs).
+Everything computes in the CUDA library behind the C ABI; there is no CPU path.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from collections import OrderedDict
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import _lib
+
+__all__ = ["random_walk", "rejection_sampling", "prepare_graph", "WalkGraph", "HostGraph",
+           "read_status", "clear_caches"]
+
+
+def _stream_handle(stream, device) -> int:
+    if stream is None:
+        return int(torch.cuda.current_stream(device).cuda_stream)
+    if isinstance(stream, torch.cuda.Stream):
+        return int(stream.cuda_stream)
+    if isinstance(stream, int):
+        return stream
+    raise TypeError(f"stream must be None, a torch.cuda.Stream or a raw handle, not {type(stream).__name__}")
+
+
+def _require(t, name, dtype, device=None):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if t.dtype != dtype:
+        # the reference reinterprets the bytes of whatever dtype it is given
+        # (random_walks/RandomWalk.cpp:33-38); here that is an error instead
+        raise TypeError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if device is not None and t.device != device:
+        raise ValueError(f"{name} is on {t.device}, expected {device}")
+    return t
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None or t.numel() == 0 else t.data_ptr()
+
+
+class WalkGraph:
+    """A CSR graph on one CUDA device plus its packed row descriptors (8 bytes per node:
+    row start | degree << 36) so that a walk step fetches row bounds with one load."""
+
+    def __init__(self, rowptr: torch.Tensor, col: torch.Tensor, *, symmetric: bool = False,
+                 use_rowdesc: bool = True, validate: bool = False, stream=None):
+        if not rowptr.is_cuda:
+            raise ValueError("WalkGraph needs CUDA tensors (use HostGraph for host arrays)")
+        dev = rowptr.device
+        self.rowptr = _require(rowptr, "rowptr", torch.int64)
+        self.col = _require(col, "col", torch.int64, dev)
+        if rowptr.dim() != 1 or rowptr.numel() < 1 or col.dim() != 1:
+            raise ValueError("rowptr must be 1-D with num_nodes + 1 entries and col 1-D")
+        self.device = dev
+        self.num_nodes = rowptr.numel() - 1
+        self.num_edges = col.numel()
+        self.symmetric = bool(symmetric)
+        self.rowdesc = None
+        self._version = (rowptr._version, col._version)
+        with torch.cuda.device(dev):
+            self.flags = torch.zeros(1, dtype=torch.int32, device=dev)
+            sh = _stream_handle(stream, dev)
+            if validate:
+                self.validate(stream=stream)
+            if use_rowdesc and self.num_nodes > 0:
+                desc = torch.empty(self.num_nodes, dtype=torch.int64, device=dev)
+                _lib.check(_lib.lib().walk_b200_rowdesc_pack(
+                    rowptr.data_ptr(), self.num_nodes, self.num_edges, desc.data_ptr(),
+                    self.flags.data_ptr(), sh))
+                f = int(self.flags.item())
+                if f & _lib.FLAG_BAD_ROWPTR:
+                    raise ValueError("rowptr is not a monotone prefix array ending at col.numel()")
+                if not (f & _lib.FLAG_DESC_OVERFLOW):
+                    self.rowdesc = desc
+                self.flags.zero_()
+
+    def csr(self) -> _lib.Csr:
+        return _lib.Csr(self.rowptr.data_ptr(), _ptr(self.col), self.num_nodes, self.num_edges,
+                        _ptr(self.rowdesc), _lib.CSR_SYMMETRIC if self.symmetric else 0, 0)
+
+    def validate(self, start: Optional[torch.Tensor] = None, *, check_sorted: bool = True, stream=None):
+        """Raise ValueError when the CSR (and, if given, the start nodes) is malformed."""
+        with torch.cuda.device(self.device):
+            flags = torch.zeros(1, dtype=torch.int32, device=self.device)
+            csr = self.csr()
+            _lib.check(_lib.lib().walk_b200_csr_validate(
+                C.byref(csr), _ptr(start), 0 if start is None else start.numel(), int(check_sorted),
+                flags.data_ptr(), _stream_handle(stream, self.device)))
+            f = int(flags.item())
+        if f:
+            raise ValueError(f"malformed graph input, status flags 0x{f:x}: {describe_flags(f)}")
+
+
+def describe_flags(f: int) -> str:
+    names = [(_lib.FLAG_BAD_NODE, "node id out of range"), (_lib.FLAG_BAD_EDGE, "edge index out of range (rand outside [0,1)?)"),
+             (_lib.FLAG_ATTEMPT_CAP, "rejection attempt cap hit"), (_lib.FLAG_BAD_ROWPTR, "rowptr malformed"),
+             (_lib.FLAG_DESC_OVERFLOW, "row descriptor overflow"), (_lib.FLAG_UNSORTED_ROW, "row not strictly ascending")]
+    return "; ".join(n for b, n in names if f & b) or "none"
+
+
+# ---- graph caches: keyed on storage identity + version, holding the keyed tensors alive
+_GRAPH_CACHE: "OrderedDict[tuple, WalkGraph]" = OrderedDict()
+_HOST_CACHE: "OrderedDict[tuple, HostGraph]" = OrderedDict()
+_CACHE_SIZE = 4
+
+
+def clear_caches() -> None:
+    _GRAPH_CACHE.clear()
+    for g in _HOST_CACHE.values():
+        g.close()
+    _HOST_CACHE.clear()
+
+
+def _key(rowptr, col, symmetric):
+    return (rowptr.data_ptr(), rowptr.numel(), rowptr._version, col.data_ptr(), col.numel(), col._version,
+            str(rowptr.device), bool(symmetric))
+
+
+def prepare_graph(rowptr, col, *, symmetric: bool = False, validate: bool = False) -> "WalkGraph":
+    """Build (or fetch from a small cache) the device-side graph for these CSR tensors."""
+    k = _key(rowptr, col, symmetric)
+    g = _GRAPH_CACHE.get(k)
+    if g is None:
+        g = WalkGraph(rowptr, col, symmetric=symmetric, validate=validate)
+        _GRAPH_CACHE[k] = g
+        while len(_GRAPH_CACHE) > _CACHE_SIZE:
+            _GRAPH_CACHE.popitem(last=False)
+    else:
+        _GRAPH_CACHE.move_to_end(k)
+    return g
+
+
+class HostGraph:
+    """A CSR graph given as host arrays, uploaded once and kept resident on one device."""
+
+    def __init__(self, rowptr, col, *, symmetric: bool = False, validate: bool = False, device=None):
+        self.rowptr = _require(_as_cpu_tensor(rowptr), "rowptr", torch.int64)
+        self.col = _require(_as_cpu_tensor(col), "col", torch.int64)
+        self.num_nodes = self.rowptr.numel() - 1
+        self.num_edges = self.col.numel()
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        h = C.c_void_p(None)
+        with torch.cuda.device(self.device):
+            _lib.check(_lib.lib().walk_b200_graph_create(
+                self.rowptr.data_ptr(), _ptr(self.col), self.num_nodes, self.num_edges,
+                _lib.CSR_SYMMETRIC if symmetric else 0, int(validate), C.byref(h)))
+        self._h = h
+
+    def device_bytes(self) -> int:
+        b = C.c_int64(0)
+        _lib.check(_lib.lib().walk_b200_graph_device_bytes(self._h, C.byref(b)))
+        return int(b.value)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            _lib.lib().walk_b200_graph_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _as_cpu_tensor(a):
+    if isinstance(a, torch.Tensor):
+        return a
+    return torch.from_numpy(np.ascontiguousarray(a))
+
+
+def _host_graph(rowptr, col, symmetric, validate):
+    k = _key(rowptr, col, symmetric)
+    g = _HOST_CACHE.get(k)
+    if g is None:
+        g = HostGraph(rowptr, col, symmetric=symmetric, validate=validate)
+        _HOST_CACHE[k] = g
+        while len(_HOST_CACHE) > _CACHE_SIZE:
+            _, old = _HOST_CACHE.popitem(last=False)
+            old.close()
+    else:
+        _HOST_CACHE.move_to_end(k)
+    return g
+
+
+def read_status(graph: WalkGraph) -> int:
+    """Synchronise and return (then clear) the status flags kernels raised on this graph."""
+    f = int(graph.flags.item())
+    if f:
+        graph.flags.zero_()
+    return f
+
+
+def _check_walk_length(walk_length):
+    if not isinstance(walk_length, (int, np.integer)) or isinstance(walk_length, bool):
+        raise TypeError("walk_length must be an int")
+    if walk_length < 0 or walk_length > 2**31 - 2:
+        raise ValueError("walk_length out of range")
+    return int(walk_length)
+
+
+def _finish(graph, out, e_out, check, return_edges):
+    if check:
+        f = read_status(graph)
+        if f:
+            raise RuntimeError(f"walk kernel raised status flags 0x{f:x}: {describe_flags(f)}")
+    return (out, e_out) if return_edges else out
+
+
+def random_walk(rowptr, col, start, rand, walk_length, *, stream=None, return_edges: bool = False,
+                check: bool = False, out: Optional[torch.Tensor] = None, graph: Optional[WalkGraph] = None):
+    """Uniform CSR random walk (``random_walk`` of the reference, ``bindings.cpp:12-21``).
+
+    Step ``l`` of walk ``w`` moves from ``v`` to ``col[rowptr[v] + int(rand[w, l] * deg(v))]``
+    with the reference's float32 arithmetic (``random_walks/RandomWalk.cpp:45-54``); a node
+    without out-edges keeps the walk in place. Returns int64 ``[n, walk_length + 1]``.
+
+    Extra keyword-only options (not in the reference): ``return_edges`` also returns the
+    edge ids ``[n, walk_length]`` the reference computes but never exposes; ``check``
+    synchronises and raises if the kernel met malformed input; ``out`` supplies the output
+    tensor; ``graph`` passes a prepared :class:`WalkGraph` instead of ``rowptr``/``col``.
+    """
+    L = _check_walk_length(walk_length)
+    if not isinstance(start, torch.Tensor) or not start.is_cuda:
+        return _random_walk_host(rowptr, col, start, rand, L, return_edges, out)
+    dev = start.device
+    g = graph if graph is not None else prepare_graph(_require(rowptr, "rowptr", torch.int64, dev),
+                                                      _require(col, "col", torch.int64, dev))
+    _require(start, "start", torch.int64, g.device)
+    _require(rand, "rand", torch.float32, g.device)
+    n = start.numel()
+    if rand.numel() != n * L:
+        raise ValueError(f"rand must hold n * walk_length = {n * L} values, has {rand.numel()}")
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty((n, L + 1), dtype=torch.int64, device=dev)
+        else:
+            _require(out, "out", torch.int64, dev)
+            if out.numel() != n * (L + 1):
+                raise ValueError("out has the wrong size")
+        e_out = torch.empty((n, L), dtype=torch.int64, device=dev) if return_edges else None
+        csr = g.csr()
+        _lib.check(_lib.lib().walk_b200_uniform_walk(
+            C.byref(csr), _ptr(start), _ptr(rand), n, L, _ptr(out), _ptr(e_out),
+            g.flags.data_ptr(), _stream_handle(stream, dev)))
+    return _finish(g, out, e_out, check, return_edges)
+
+
+def rejection_sampling(rowptr, col, start, walk_length, p, q, *, stream=None, seed: int = 0,
+                       walk_index_base: int = 0, symmetric: bool = False, return_edges: bool = False,
+                       return_counters: bool = False, check: bool = False,
+                       out: Optional[torch.Tensor] = None, graph: Optional[WalkGraph] = None):
+    """node2vec biased walk by rejection sampling (``rejection_sampling`` of the reference,
+    ``bindings.cpp:35-45``; loop at ``random_walks/BiasedRandomWalk.cpp:52-99``).
+
+    The reference draws from the C library's global ``rand()``; here the draws are a
+    Philox4x32-10 stream keyed by ``seed`` and indexed by (global walk index, step,
+    attempt), so a call is reproducible, re-entrant and independent of how walks are
+    sharded (``walk_index_base`` = global index of row 0 of this call). Every row of
+    ``col`` must be sorted ascending. ``symmetric=True`` asserts an undirected graph and
+    lets the membership test search the previous node's row; results do not change.
+    Returns int64 ``[n, walk_length + 1]``.
+    """
+    L = _check_walk_length(walk_length)
+    p, q = float(p), float(q)
+    if not isinstance(start, torch.Tensor) or not start.is_cuda:
+        return _rejection_sampling_host(rowptr, col, start, L, p, q, seed, walk_index_base, symmetric,
+                                        return_edges, out)
+    dev = start.device
+    g = graph if graph is not None else prepare_graph(_require(rowptr, "rowptr", torch.int64, dev),
+                                                      _require(col, "col", torch.int64, dev),
+                                                      symmetric=symmetric)
+    _require(start, "start", torch.int64, g.device)
+    n = start.numel()
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty((n, L + 1), dtype=torch.int64, device=dev)
+        else:
+            _require(out, "out", torch.int64, dev)
+            if out.numel() != n * (L + 1):
+                raise ValueError("out has the wrong size")
+        e_out = torch.empty((n, L), dtype=torch.int64, device=dev) if return_edges else None
+        counters = torch.zeros(len(_lib.COUNTER_NAMES), dtype=torch.int64, device=dev) if return_counters else None
+        csr = g.csr()
+        _lib.check(_lib.lib().walk_b200_node2vec_walk(
+            C.byref(csr), _ptr(start), n, L, p, q, int(seed) & (2**64 - 1), int(walk_index_base),
+            _ptr(out), _ptr(e_out), g.flags.data_ptr(), _ptr(counters), _stream_handle(stream, dev)))
+    res = _finish(g, out, e_out, check, return_edges)
+    if return_counters:
+        cnt = dict(zip(_lib.COUNTER_NAMES, (int(x) for x in counters.tolist())))
+        return (*res, cnt) if isinstance(res, tuple) else (res, cnt)
+    return res
+
+
+# ---- host-array path ---------------------------------------------------------------
+
+def _host_out(n, L, out):
+    if out is None:
+        return torch.empty((n, L + 1), dtype=torch.int64, pin_memory=True)
+    _require(out, "out", torch.int64)
+    if out.is_cuda or out.numel() != n * (L + 1):
+        raise ValueError("out must be a CPU int64 tensor of n * (walk_length + 1) elements")
+    return out
+
+
+def _random_walk_host(rowptr, col, start, rand, L, return_edges, out):
+    rowptr, col = _as_cpu_tensor(rowptr), _as_cpu_tensor(col)
+    start = _require(_as_cpu_tensor(start), "start", torch.int64)
+    rand = _require(_as_cpu_tensor(rand), "rand", torch.float32)
+    n = start.numel()
+    if rand.numel() != n * L:
+        raise ValueError(f"rand must hold n * walk_length = {n * L} values, has {rand.numel()}")
+    g = _host_graph(rowptr, col, False, False)
+    out = _host_out(n, L, out)
+    e_out = torch.empty((n, L), dtype=torch.int64, pin_memory=True) if return_edges else None
+    with torch.cuda.device(g.device):
+        _lib.check(_lib.lib().walk_b200_uniform_walk_host(g._h, _ptr(start), _ptr(rand), n, L, _ptr(out), _ptr(e_out)))
+    return (out, e_out) if return_edges else out
+
+
+def _rejection_sampling_host(rowptr, col, start, L, p, q, seed, base, symmetric, return_edges, out):
+    rowptr, col = _as_cpu_tensor(rowptr), _as_cpu_tensor(col)
+    start = _require(_as_cpu_tensor(start), "start", torch.int64)
+    n = start.numel()
+    g = _host_graph(rowptr, col, symmetric, False)
+    out = _host_out(n, L, out)
+    e_out = torch.empty((n, L), dtype=torch.int64, pin_memory=True) if return_edges else None
+    with torch.cuda.device(g.device):
+        _lib.check(_lib.lib().walk_b200_node2vec_walk_host(g._h, _ptr(start), n, L, p, q, int(seed) & (2**64 - 1),
+                                                           int(base), _ptr(out), _ptr(e_out)))
+    return (out, e_out) if return_edges else out

@@ -1,0 +1,110 @@
+"""Sharding layer: start rows split across ranks, one process per GPU.
+
+Walks are independent, the CSR is replicated in every GPU's memory and read-only, so
+the walk itself needs no collective: rank ``r`` of ``G`` walks the contiguous block of
+start rows ``shard_range(n, G, r)``. node2vec draws are indexed by the *global* row, so
+the union of the shards is bit-identical to a single-GPU run whatever ``G`` is. The one
+optional exchange is the gather of the walk matrix to one rank, done with point-to-point
+sends posted as one batch (rows land at their global offset; the destination rank's own
+walk kernel writes straight into its slice of the gathered matrix).
+
+The reference has no counterpart: it is a single-device library.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+def shard_range(num_walks: int, world_size: int, rank: int):
+    """Rows ``[begin, end)`` of rank ``rank``: blocks of ``ceil(n / world_size)`` rows."""
+    return _lib.shard_range(num_walks, world_size, rank)
+
+
+def _world(group):
+    if dist.is_available() and dist.is_initialized():
+        return dist.get_world_size(group), dist.get_rank(group)
+    return 1, 0
+
+
+def gather_rows(shard: torch.Tensor, num_rows: int, *, group=None, dst: int = 0,
+                out: Optional[torch.Tensor] = None, chunk_rows: int = 1 << 22):
+    """Collect row shards (``shard_range`` layout) on rank ``dst``.
+
+    Returns the ``[num_rows, width]`` matrix on ``dst`` and ``None`` elsewhere. When
+    ``out`` is given on ``dst`` and ``shard`` already is the matching slice of ``out``,
+    no local copy is made. Messages are cut into pieces of ``chunk_rows`` rows.
+    """
+    world, rank = _world(group)
+    width = shard.shape[1]
+    if world == 1:
+        if out is None:
+            return shard
+        if out.data_ptr() != shard.data_ptr():
+            out.copy_(shard)
+        return out
+    ops = []
+    if rank == dst:
+        if out is None:
+            out = torch.empty((num_rows, width), dtype=shard.dtype, device=shard.device)
+        b, e = shard_range(num_rows, world, rank)
+        mine = out[b:e]
+        if mine.data_ptr() != shard.data_ptr():
+            mine.copy_(shard)
+        for r in range(world):
+            if r == dst:
+                continue
+            rb, re = shard_range(num_rows, world, r)
+            for c0 in range(rb, re, chunk_rows):
+                c1 = min(re, c0 + chunk_rows)
+                ops.append(dist.P2POp(dist.irecv, out[c0:c1], dist.get_global_rank(group, r) if group else r, group))
+    else:
+        b, e = shard_range(num_rows, world, rank)
+        assert shard.shape[0] == e - b, "shard does not match shard_range"
+        for c0 in range(0, e - b, chunk_rows):
+            c1 = min(e - b, c0 + chunk_rows)
+            ops.append(dist.P2POp(dist.isend, shard[c0:c1], dist.get_global_rank(group, dst) if group else dst, group))
+    if ops:
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+    return out if rank == dst else None
+
+
+def sharded_walk(op: Callable[..., torch.Tensor], start: torch.Tensor, walk_length: int, *,
+                 rand: Optional[torch.Tensor] = None, group=None, gather: bool = False, dst: int = 0,
+                 start_is_sharded: bool = False, num_walks: Optional[int] = None):
+    """Run ``op`` on this rank's block of start rows.
+
+    ``op(start_shard, rand_shard, walk_index_base, out)`` must return the ``[rows,
+    walk_length + 1]`` matrix (written into ``out`` when ``out`` is not None); the product
+    callers pass a closure over :func:`random_walk` / :func:`rejection_sampling`.
+    ``start`` (and ``rand``) are either the full arrays, replicated on every rank
+    (default), or already this rank's block (``start_is_sharded=True`` with ``num_walks``
+    = global row count). Returns ``(shard, (begin, end))`` or, with ``gather=True``,
+    ``(full matrix on dst / None elsewhere, (begin, end))``.
+    """
+    world, rank = _world(group)
+    n = int(num_walks) if start_is_sharded else start.shape[0]
+    if start_is_sharded and num_walks is None:
+        raise ValueError("num_walks is required when start is already sharded")
+    b, e = shard_range(n, world, rank)
+    if start_is_sharded:
+        if start.shape[0] != e - b:
+            raise ValueError(f"rank {rank} expects {e - b} start rows, got {start.shape[0]}")
+        s_shard, r_shard = start, rand
+    else:
+        s_shard = start[b:e]
+        r_shard = None if rand is None else rand.reshape(n, -1)[b:e]
+    out_view = None
+    full = None
+    if gather and rank == dst and world > 1:
+        full = torch.empty((n, walk_length + 1), dtype=torch.int64, device=start.device)
+        out_view = full[b:e]
+    shard = op(s_shard, r_shard, b, out_view)
+    if not gather:
+        return shard, (b, e)
+    return gather_rows(shard, n, group=group, dst=dst, out=full), (b, e)
