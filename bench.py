@@ -1,0 +1,449 @@
+#!/usr/bin/env python
+"""Throughput bench of the walk path: walk steps per second on seeded synthetic graphs.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+A "step" is one pass of the walk generator over one batch of start nodes. The default
+workload is the node2vec one the headline metric is quoted on (R-MAT scale 24, edge
+factor 16, every node a start, walk_length 80, p=0.25, q=4, Philox draws); start rows
+are sharded over the ranks, the CSR is replicated per GPU. One JSON line is printed by
+rank 0. With ``--impl reference`` the reference's own CPU loops are timed instead, on
+the host cores, on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOADS = {
+    # name: kind, scale, edge_factor, graph seed, walk_length, p, q
+    "node2vec_rmat24": dict(kind="node2vec", scale=24, edge_factor=16, seed=2, L=80, p=0.25, q=4.0),
+    "uniform_rmat22": dict(kind="uniform", scale=22, edge_factor=16, seed=1, L=80),
+    "node2vec_rmat20": dict(kind="node2vec", scale=20, edge_factor=16, seed=2, L=80, p=0.25, q=4.0),
+    "uniform_rmat20": dict(kind="uniform", scale=20, edge_factor=16, seed=1, L=80),
+    "node2vec_rmat22_p1q2": dict(kind="node2vec", scale=22, edge_factor=16, seed=3, L=40, p=1.0, q=2.0),
+}
+RMAT = dict(a=0.57, b=0.19, c=0.19, d=0.05)
+PHILOX_SEED = 20240607
+
+
+def env_rank():
+    return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+
+
+def measured_peak_gbs():
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        try:
+            return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    """Samples SM clock, power and throttle reasons of one GPU with nvidia-smi while the
+    timed region runs (reading only; no setting is touched)."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.rows, self.proc, self.t0, self.t1 = [], None, None, None
+        try:
+            uuid = str(torch.cuda.get_device_properties(device).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", uuid, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), line.strip()))
+
+    def mark_start(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        time.sleep(0.06)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        inside = [r for t, r in self.rows if self.t0 is not None and self.t0 <= t <= (self.t1 or t) + 0.05]
+        use = inside or [r for _, r in self.rows]
+        sm, mx, pw, reasons = [], [], [], set()
+        for r in use:
+            p = [x.strip() for x in r.split(",")]
+            if len(p) < 7:
+                continue
+            try:
+                sm.append(float(p[0])); mx.append(float(p[1])); pw.append(float(p[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(pw) if pw else None, "reasons": sorted(reasons),
+                "samples": len(use), "samples_in_timed_region": len(inside)}
+
+
+# ------------------------------------------------------------------------------ graph
+def build_graph(wl, device, world, rank):
+    """Rank 0 builds the seeded R-MAT CSR on its GPU; other ranks receive a replica."""
+    from mlx_cluster_b200 import graphs
+    import torch.distributed as dist
+    t0 = time.time()
+    if rank == 0:
+        rowptr, col = graphs.rmat_csr(wl["scale"], wl["edge_factor"], seed=wl["seed"], device=device, **RMAT)
+        torch.cuda.synchronize(device)
+    if world > 1:
+        meta = torch.tensor([rowptr.numel(), col.numel()] if rank == 0 else [0, 0], dtype=torch.int64, device=device)
+        dist.broadcast(meta, 0)
+        if rank != 0:
+            rowptr = torch.empty(int(meta[0]), dtype=torch.int64, device=device)
+            col = torch.empty(int(meta[1]), dtype=torch.int64, device=device)
+        dist.broadcast(rowptr, 0)
+        dist.broadcast(col, 0)
+        torch.cuda.synchronize(device)
+    torch.cuda.empty_cache()
+    return rowptr, col, time.time() - t0
+
+
+# ------------------------------------------------------------------------------ CPU reference legs
+_CPU_CTX = {}  # arrays the forked CPU workers read (inherited by fork, never pickled)
+
+
+def _cpu_worker(job):
+    import oracle
+    kind_impl, b, e, seed = job
+    c = _CPU_CTX
+    start = c["start"][b:e]
+    rand = None if c["rand"] is None else c["rand"][b:e]
+    t = time.perf_counter()
+    if kind_impl == "reference":
+        if c["kind"] == "uniform":
+            oracle.ref_random_walk(c["rowptr"], c["col"], start, rand, c["L"])
+        else:
+            oracle.ref_rejection_sampling(c["rowptr"], c["col"], start, c["L"], c["p"], c["q"], srand_seed=seed)
+    else:
+        if c["kind"] == "uniform":
+            oracle.uniform_walk(c["rowptr"], c["col"], start, rand, c["L"])
+        else:
+            oracle.node2vec_walk(c["rowptr"], c["col"], start, c["L"], c["p"], c["q"], seed=seed)
+    return time.perf_counter() - t
+
+
+def cpu_walk_seconds(wl, rowptr, col, start, rand, procs):
+    """Wall seconds for the reference CPU loop over `start`, split over `procs` processes
+    (the reference loop is serial and draws from the global rand(), so processes, not threads)."""
+    import oracle
+    kind_impl = "reference" if oracle.have_ref() else "port"
+    _CPU_CTX.update(rowptr=rowptr, col=col, start=start, rand=rand, kind=wl["kind"], L=wl["L"],
+                    p=wl.get("p", 1.0), q=wl.get("q", 1.0))
+    n = start.shape[0]
+    per = -(-n // procs)
+    jobs = [(kind_impl, i * per, min(n, (i + 1) * per), 1 + i) for i in range(procs) if i * per < n]
+    t = time.perf_counter()
+    if len(jobs) == 1:
+        _cpu_worker(jobs[0])
+    else:
+        import multiprocessing as mp
+        with mp.get_context("fork").Pool(len(jobs)) as pool:
+            pool.map(_cpu_worker, jobs, chunksize=1)
+    return time.perf_counter() - t, kind_impl, len(jobs)
+
+
+def size_cpu_sample(wl, rowptr, col, n_total, target_s, procs, rng):
+    """Pick how many of the workload's first start rows give about target_s of CPU work."""
+    pilot = min(n_total, 2048 * procs)
+    start = np.arange(pilot, dtype=np.int64)
+    rand = rng.random((pilot, wl["L"]), dtype=np.float32) if wl["kind"] == "uniform" else None
+    secs, _, _ = cpu_walk_seconds(wl, rowptr, col, start, rand, procs)
+    rows = int(min(n_total, max(pilot, pilot * target_s / max(secs, 1e-6))))
+    return rows
+
+
+def run_reference_arm(args, wl):
+    rank, local_rank, world = env_rank()
+    if rank != 0:
+        return 0
+    from mlx_cluster_b200 import graphs
+    dev = torch.device("cuda", local_rank) if torch.cuda.is_available() else torch.device("cpu")
+    rowptr, col = graphs.rmat_csr(wl["scale"], wl["edge_factor"], seed=wl["seed"], device=dev, **RMAT)
+    rowptr, col = rowptr.cpu().numpy(), col.cpu().numpy()
+    n_total, L = rowptr.size - 1, wl["L"]
+    procs = len(os.sched_getaffinity(0))
+    rng = np.random.default_rng(0)
+    budget_s = 150.0
+    per_step = budget_s / max(1, args.steps + args.warmup)
+    rows = size_cpu_sample(wl, rowptr, col, n_total, per_step, procs, rng)
+    start = np.arange(rows, dtype=np.int64)
+    rand = rng.random((rows, L), dtype=np.float32) if wl["kind"] == "uniform" else None
+    kind, used = "port", procs
+    for _ in range(args.warmup):
+        cpu_walk_seconds(wl, rowptr, col, start, rand, procs)
+    t = time.perf_counter()
+    for _ in range(args.steps):
+        _, kind, used = cpu_walk_seconds(wl, rowptr, col, start, rand, procs)
+    total = time.perf_counter() - t
+    value = rows * L * args.steps / total
+    sample = f"first {rows} of {n_total} start rows per step, {used} processes, process start-up included"
+    line = {
+        "impl": "reference", "metric": "walk_steps_per_sec", "value": value, "unit": "steps/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+        "config": workload_config(wl, n_total, int(col.size), args.gpus),
+        "cpu_baseline": {"value": value, "unit": "steps/s", "cores": used, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": "steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def workload_config(wl, n_nodes, n_edges, gpus):
+    c = {"workload": args_workload_name(wl), "graph": f"R-MAT scale {wl['scale']} edge factor {wl['edge_factor']} "
+         f"(a,b,c,d)=(0.57,0.19,0.19,0.05) seed {wl['seed']}, symmetrised, deduplicated, no self-loops, int64 CSR",
+         "num_nodes": n_nodes, "num_directed_edges": n_edges, "starts": "every node once", "walk_length": wl["L"],
+         "sharding": f"start rows over {gpus} GPU(s), CSR replicated",
+         "l2": "no flush between steps: col (8 B x edges) is far larger than the 126 MB L2"}
+    if wl["kind"] == "node2vec":
+        c.update(p=wl["p"], q=wl["q"], draws="Philox4x32-10, key=seed, counter=(walk,step,attempt)")
+    else:
+        c.update(rand="float32 uniform [0,1) [n, walk_length], caller-supplied")
+    return c
+
+
+def args_workload_name(wl):
+    for k, v in WORKLOADS.items():
+        if v is wl:
+            return k
+    return "custom"
+
+
+# ------------------------------------------------------------------------------ GPU arm
+def time_launches(fn, steps, warmup, stream, sampler=None, barrier=None):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if barrier:
+        barrier()
+    torch.cuda.synchronize()
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    if sampler:
+        sampler.mark_start()
+    from mlx_cluster_b200 import _lib
+    launches = _lib.launch_count()
+    evs[0].record(stream)
+    for i in range(steps):
+        fn()
+        evs[i + 1].record(stream)
+    torch.cuda.synchronize()
+    launches = _lib.launch_count() - launches
+    if sampler:
+        sampler.mark_end()
+    if barrier:
+        barrier()
+    per = [evs[i].elapsed_time(evs[i + 1]) for i in range(steps)]
+    return evs[0].elapsed_time(evs[steps]), per, launches
+
+
+def run_ours(args, wl):
+    import torch.distributed as dist
+    from mlx_cluster_b200 import _lib, random_walk, rejection_sampling
+    from mlx_cluster_b200.ops import WalkGraph, HostGraph
+    from mlx_cluster_b200.sharding import shard_range
+
+    rank, local_rank, world = env_rank()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this package has no CPU path")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    barrier = (lambda: dist.barrier()) if world > 1 else None
+
+    def allmax(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def allsum(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return float(t.item())
+
+    _lib.lib()  # fail now if the CUDA library is missing
+    rowptr, col, build_s = build_graph(wl, dev, world, rank)
+    n_nodes, n_edges, L = rowptr.numel() - 1, col.numel(), wl["L"]
+    b, e = shard_range(n_nodes, world, rank)
+    rows = e - b
+    start = torch.arange(b, e, dtype=torch.int64, device=dev)
+    graph = WalkGraph(rowptr, col, symmetric=True)
+    out = torch.empty((rows, L + 1), dtype=torch.int64, device=dev)
+    stream = torch.cuda.current_stream(dev)
+
+    if wl["kind"] == "node2vec":
+        # untimed instrumented pass: counts the 8-byte gathers this batch needs
+        _, cnt = rejection_sampling(None, None, start, L, wl["p"], wl["q"], graph=graph, seed=PHILOX_SEED,
+                                    walk_index_base=b, out=out, return_counters=True, check=True)
+        loads = cnt["loads"]
+        alg_bytes = 8 * loads + 8 * rows * (L + 1) + 8 * rows  # gathers + walk matrix + start
+        rand = None
+
+        def step():
+            rejection_sampling(None, None, start, L, wl["p"], wl["q"], graph=graph, seed=PHILOX_SEED,
+                               walk_index_base=b, out=out)
+    else:
+        gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+        rand = torch.rand((rows, L), generator=gen, device=dev)
+        deg = rowptr.diff()
+        cnt = {}
+        random_walk(None, None, start, rand, L, graph=graph, out=out, check=True)
+        moved = int((deg[out[:, :-1].reshape(-1)] > 0).sum().item())
+        stay = rows * L - moved
+        # per step: row bounds 16 (8 via the packed descriptor, counted as the CSR's 16) + rand 4 + col 8 + out 8
+        alg_bytes = rows * 16 + moved * 36 + stay * 24
+
+        def step():
+            random_walk(None, None, start, rand, L, graph=graph, out=out)
+
+    sampler = ClockSampler(dev) if rank == 0 else None
+    total_ms, per, timed_launches = time_launches(step, args.steps, args.warmup, stream, sampler, barrier)
+    clocks = sampler.stop() if sampler else None
+    ms_per_step = allmax(total_ms / args.steps)
+    kernel_ms = statistics.mean(per)
+    value = n_nodes * L / (ms_per_step * 1e-3)
+    peak, peak_kind = measured_peak_gbs()
+    achieved = allsum(alg_bytes / (kernel_ms * 1e-3) / 1e9) / world  # mean per-GPU GB/s
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "peak_source": f"of {peak_kind}", "traffic": None, "kernel": "node2vec_walk_kernel" if
+                wl["kind"] == "node2vec" else "uniform_walk_staged_kernel", "kernel_ms": kernel_ms,
+                "algorithmic_bytes_per_launch": alg_bytes,
+                "algorithmic_bytes_per_walk_step": alg_bytes / max(1, rows * L)}
+    if cnt:
+        roofline["counters"] = cnt
+
+    # ---- end to end: host buffers through the public API, copies inside the timed region
+    e2e = None
+    if not args.no_e2e:
+        e2e_steps = max(1, min(args.steps, args.e2e_steps))
+        h_rowptr, h_col = rowptr.cpu(), col.cpu()
+        h_start = start.cpu().pin_memory()
+        h_out = torch.empty((rows, L + 1), dtype=torch.int64, pin_memory=True)
+        h_rand = rand.cpu().pin_memory() if rand is not None else None
+        t_up = time.perf_counter()
+        hg = HostGraph(h_rowptr, h_col, symmetric=True, device=dev)
+        upload_s = time.perf_counter() - t_up
+        del graph, out
+        torch.cuda.empty_cache()
+
+        def host_step():
+            if wl["kind"] == "node2vec":
+                _lib.check(_lib.lib().walk_b200_node2vec_walk_host(
+                    hg._h, h_start.data_ptr(), rows, L, wl["p"], wl["q"], PHILOX_SEED, b, h_out.data_ptr(), None))
+            else:
+                _lib.check(_lib.lib().walk_b200_uniform_walk_host(
+                    hg._h, h_start.data_ptr(), h_rand.data_ptr(), rows, L, h_out.data_ptr(), None))
+
+        host_step()
+        if barrier:
+            barrier()
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            host_step()
+        dt = time.perf_counter() - t0
+        e2e_ms = allmax(1e3 * dt / e2e_steps)
+        e2e = {"value": n_nodes * L / (e2e_ms * 1e-3), "unit": "steps/s",
+               "h2d_bytes_per_step": int(allsum(rows * 8 + (rows * L * 4 if rand is not None else 0))),
+               "d2h_bytes_per_step": int(allsum(rows * (L + 1) * 8)), "ms_per_step": e2e_ms, "steps": e2e_steps,
+               "api": "walk_b200_*_walk_host (C ABI, pinned host buffers, graph resident)",
+               "graph_upload_s_once": upload_s}
+        hg.close()
+
+    # ---- CPU baseline beside it (rank 0, single GPU runs only)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        rp, cl = rowptr.cpu().numpy(), col.cpu().numpy()
+        rng = np.random.default_rng(0)
+        n_rows = size_cpu_sample(wl, rp, cl, n_nodes, args.cpu_seconds, 1, rng)
+        s = np.arange(n_rows, dtype=np.int64)
+        r = rng.random((n_rows, L), dtype=np.float32) if wl["kind"] == "uniform" else None
+        secs, kind, used = cpu_walk_seconds(wl, rp, cl, s, r, 1)
+        cpu = {"value": n_rows * L / secs, "unit": "steps/s", "cores": used, "kind": kind,
+               "sample": f"first {n_rows} of {n_nodes} start rows, one pass, {secs:.1f} s",
+               "host_cores_available": len(os.sched_getaffinity(0))}
+
+    if rank == 0:
+        line = {
+            "metric": "walk_steps_per_sec", "value": value, "unit": "steps/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+            "config": workload_config(wl, n_nodes, n_edges, world), "roofline": roofline, "cpu_baseline": cpu,
+            "e2e": e2e, "gpu_launches": int(timed_launches), "clocks": clocks, "graph_build_s": build_s,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="node2vec_rmat24", choices=list(WORKLOADS))
+    ap.add_argument("--e2e-steps", type=int, default=3, help="end-to-end passes (each moves the whole walk matrix to the host)")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target CPU time of the cpu_baseline sample")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--tune", action="append", default=[], help="key=value passed to walk_b200_set_tuning")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        return run_reference_arm(args, wl)
+    if args.tune:
+        from mlx_cluster_b200 import _lib
+        for kv in args.tune:
+            k, v = kv.split("=")
+            _lib.set_tuning(k, int(v))
+    return run_ours(args, wl)
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

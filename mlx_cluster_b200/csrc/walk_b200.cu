@@ -319,7 +319,10 @@ int walk_b200_l2_window_set(const void* ptr, size_t bytes, float hit_ratio, void
   CUDA_TRY(cudaDeviceGetAttribute(&max_window, cudaDevAttrMaxAccessPolicyWindowSize, dev));
   CUDA_TRY(cudaDeviceGetAttribute(&max_persist, cudaDevAttrMaxPersistingL2CacheSize, dev));
   if (max_window <= 0 || max_persist <= 0) return WALK_B200_OK;  // nothing on offer: not an error
-  CUDA_TRY(cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, (size_t)max_persist));
+  if (cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, (size_t)max_persist) != cudaSuccess) {
+    (void)cudaGetLastError();  // carve-out refused (e.g. a shared-context configuration): run without the hint
+    return WALK_B200_OK;
+  }
   size_t win = bytes < (size_t)max_window ? bytes : (size_t)max_window;
   cudaStreamAttrValue attr;
   memset(&attr, 0, sizeof(attr));

@@ -1,0 +1,97 @@
+"""Host-buffer entry points of the C ABI (resident graph + slab pipeline) against the
+CPU restatement, and the L2 residency hint."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from mlx_cluster_b200 import _lib, clear_caches, random_walk, rejection_sampling
+from mlx_cluster_b200.ops import HostGraph, WalkGraph
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(autouse=True)
+def _reset():
+    yield
+    _lib.set_tuning("host_slab_mb", 256)
+    clear_caches()
+
+
+def test_host_arrays_uniform_and_biased(cuda, golden):
+    g = golden
+    out = random_walk(g["rowptr1"], g["col1"], g["start1"], g["rand1"], 5)
+    assert not out.is_cuda
+    np.testing.assert_array_equal(out.numpy(), g["uniform1_n"])
+    out, e = random_walk(torch.from_numpy(g["rowptr2"]), torch.from_numpy(g["col2"]), torch.from_numpy(g["start2"]),
+                         torch.from_numpy(g["rand2"]), 20, return_edges=True)
+    np.testing.assert_array_equal(out.numpy(), g["uniform2_n"])
+    np.testing.assert_array_equal(e.numpy(), g["uniform2_e"])
+    for sym in (False, True):
+        out = rejection_sampling(g["rowptr2"], g["col2"], g["start2"], 20, 0.5, 2.0, seed=4, symmetric=sym)
+        np.testing.assert_array_equal(out.numpy(), oracle.node2vec_walk(g["rowptr2"], g["col2"], g["start2"], 20,
+                                                                        0.5, 2.0, seed=4))
+
+
+def test_slab_pipeline_many_slabs(cuda):
+    """Force several slabs per lane: results must not depend on the slab size, and node2vec
+    rows keep their global walk index across slabs."""
+    from mlx_cluster_b200 import graphs
+    rowptr, col = graphs.rmat_csr(12, 8, seed=3)
+    n_nodes = rowptr.numel() - 1
+    rng = np.random.default_rng(1)
+    walks, L = 50000, 24
+    start = torch.from_numpy(rng.integers(0, n_nodes, walks).astype(np.int64)).pin_memory()
+    rand = torch.from_numpy(rng.random((walks, L), dtype=np.float32)).pin_memory()
+    want_u = oracle.uniform_walk(rowptr.numpy(), col.numpy(), start.numpy(), rand.numpy(), L)
+    want_b = oracle.node2vec_walk(rowptr.numpy(), col.numpy(), start.numpy(), L, 0.25, 4.0, seed=8, walk_index_base=17)
+    for slab_mb in (1, 3, 256):
+        _lib.set_tuning("host_slab_mb", slab_mb)
+        before = _lib.launch_count()
+        out = random_walk(rowptr, col, start, rand, L)
+        launches = _lib.launch_count() - before
+        np.testing.assert_array_equal(out.numpy(), want_u)
+        if slab_mb == 1:
+            assert launches >= 8
+        out = rejection_sampling(rowptr, col, start, L, 0.25, 4.0, seed=8, walk_index_base=17, symmetric=True)
+        np.testing.assert_array_equal(out.numpy(), want_b)
+
+
+def test_host_entry_reports_bad_input(cuda, golden):
+    g = golden
+    start = g["start1"].copy()
+    start[5] = 99999
+    with pytest.raises(_lib.WalkError) as ei:
+        random_walk(g["rowptr1"], g["col1"], start, g["rand1"], 5)
+    assert ei.value.code == _lib.ERR_DEVICE_FLAGS and "node id out of range" in str(ei.value)
+    bad_rowptr = g["rowptr1"].copy()
+    bad_rowptr[100] = bad_rowptr[99] - 1
+    with pytest.raises(_lib.WalkError) as ei:
+        HostGraph(bad_rowptr, g["col1"])
+    assert ei.value.code == _lib.ERR_CSR_INVALID
+    unsorted = g["col1"].copy()
+    r = int(np.argmax(np.diff(g["rowptr1"]) >= 2))
+    a = g["rowptr1"][r]
+    unsorted[a], unsorted[a + 1] = unsorted[a + 1], unsorted[a]
+    with pytest.raises(_lib.WalkError):
+        HostGraph(g["rowptr1"], unsorted, validate=True)
+    hg = HostGraph(g["rowptr1"], g["col1"], validate=True)
+    assert hg.device_bytes() == (2709 + 10556 + 2708) * 8
+    hg.close()
+
+
+def test_l2_window_hint_does_not_change_results(cuda, golden):
+    g = golden
+    t = lambda a: torch.from_numpy(a).to(cuda)
+    graph = WalkGraph(t(g["rowptr1"]), t(g["col1"]))
+    s = torch.cuda.Stream(cuda)
+    granted = C.c_size_t(0)
+    _lib.check(_lib.lib().walk_b200_l2_window_set(graph.rowdesc.data_ptr(), graph.rowdesc.numel() * 8, 1.0,
+                                                  s.cuda_stream, C.byref(granted)))
+    out = random_walk(None, None, t(g["start1"]), t(g["rand1"]), 5, graph=graph, stream=s)
+    s.synchronize()
+    np.testing.assert_array_equal(out.cpu().numpy(), g["uniform1_n"])
+    _lib.check(_lib.lib().walk_b200_l2_window_clear(s.cuda_stream))
+    assert granted.value in (0, graph.rowdesc.numel() * 8)
