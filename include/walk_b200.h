@@ -182,6 +182,38 @@ int walk_b200_l2_window_set(const void* ptr, size_t bytes, float hit_ratio, void
                             size_t* granted_bytes);
 int walk_b200_l2_window_clear(void* stream);
 
+/* ---- entry point that allocates nothing ----------------------------------------
+ * No counterpart in the reference (its primitives always allocate their outputs and
+ * know nothing of scratch memory).
+ *
+ * Same walk, same results as walk_b200_uniform_walk with a packed row descriptor, for
+ * callers that must not allocate device memory at call time: code that runs where a
+ * cudaMalloc would stall the device it shares with latency-critical work (cudaMalloc
+ * synchronises the whole device), hosts whose own memory pool already owns all of the
+ * GPU so that a driver allocation may simply fail, and plug-in layers that are only
+ * handed raw pointers and have no allocator to ask. Such a caller still passes the
+ * CSR, the inputs and the outputs; the one piece of scratch the fast path needs -- the
+ * 8-byte row descriptor per node -- lives in a fixed array inside the library's own
+ * device image (WALK_B200_NOALLOC_MAX_NODES entries = 8 MiB, resident on every GPU
+ * that loads the library until the process exits). The call packs rowptr into that
+ * array and then walks, both on `stream`; it calls no cudaMalloc / cudaFree / pool
+ * routine. Graphs with more than WALK_B200_NOALLOC_MAX_NODES nodes (or more than 2^36
+ * edges) are rejected with WALK_B200_ERR_UNSUPPORTED.
+ *
+ * The first call on each device looks up the array's device address (a one-off
+ * set-up that may make the driver load this library's device code), so make that
+ * first call outside of any stream capture. All calls on a device share the one
+ * array and it keeps the previous call's descriptors: every call rewrites the
+ * entries it reads before reading them, so nothing has to be cleared, but two calls
+ * whose work overlaps on the GPU (different streams, no ordering between them) race
+ * on it -- order them. e_out and status_flags may be NULL.
+ */
+#define WALK_B200_NOALLOC_MAX_NODES (1 << 20)
+int walk_b200_uniform_walk_noalloc(const int64_t* rowptr, const int64_t* col, int64_t num_nodes,
+                                   int64_t num_edges, const int64_t* start, const float* rand,
+                                   int64_t num_walks, int32_t walk_length, int64_t* n_out,
+                                   int64_t* e_out, uint32_t* status_flags, void* stream);
+
 /* Kernel variant selection for experiments ("uniform_chunk", "n2v_block", ...); unknown keys fail. */
 int walk_b200_set_tuning(const char* key, int32_t value);
 int walk_b200_get_tuning(const char* key, int32_t* value);

@@ -29,7 +29,9 @@ EXPORTS = (
     "walk_b200_graph_device_bytes", "walk_b200_uniform_walk_host", "walk_b200_node2vec_walk_host",
     "walk_b200_l2_window_set", "walk_b200_l2_window_clear",
     "walk_b200_set_tuning", "walk_b200_get_tuning",
+    "walk_b200_uniform_walk_noalloc",
 )
+NOALLOC_MAX_NODES = 1 << 20
 
 
 class Csr(C.Structure):
@@ -78,6 +80,7 @@ def lib():
     L.walk_b200_node2vec_walk_host.argtypes = [vp, vp, i64, i32, dbl, dbl, u64, u64, vp, vp]
     L.walk_b200_l2_window_set.argtypes = [vp, C.c_size_t, C.c_float, vp, C.POINTER(C.c_size_t)]
     L.walk_b200_l2_window_clear.argtypes = [vp]
+    L.walk_b200_uniform_walk_noalloc.argtypes = [vp, vp, i64, i64, vp, vp, i64, i32, vp, vp, vp, vp]
     L.walk_b200_set_tuning.argtypes = [C.c_char_p, i32]
     L.walk_b200_get_tuning.argtypes = [C.c_char_p, C.POINTER(i32)]
     for name in EXPORTS:  # AttributeError here = the built library is older than the header

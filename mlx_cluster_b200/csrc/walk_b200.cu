@@ -355,6 +355,73 @@ int walk_b200_l2_window_clear(void* stream) {
 }  // extern "C"
 
 // ======================================================================================
+// Entry point that allocates nothing
+// ======================================================================================
+// Scratch for callers that cannot allocate: the packed row descriptors live in this
+// fixed array of the library's device image instead of caller or pool memory. In host
+// code the name below is only a handle for the runtime, never a device address; the
+// address each device gave the array is looked up once and cached in noalloc_scratch().
+static __device__ __align__(256) unsigned long long g_noalloc_rowdesc[WALK_B200_NOALLOC_MAX_NODES];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+uint64_t* g_noalloc_ptr[kMaxDevices] = {};
+
+// Device address of g_noalloc_rowdesc on the current device (set-up on first use).
+int noalloc_scratch(uint64_t** out) {
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(WALK_B200_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (!g_noalloc_ptr[dev]) {
+    void* p = nullptr;
+    CUDA_TRY(cudaGetSymbolAddress(&p, g_noalloc_rowdesc));
+    if (!p) return fail(WALK_B200_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    g_noalloc_ptr[dev] = static_cast<uint64_t*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return WALK_B200_OK;
+}
+
+}  // namespace
+
+extern "C" int walk_b200_uniform_walk_noalloc(const int64_t* rowptr, const int64_t* col, int64_t num_nodes,
+                                              int64_t num_edges, const int64_t* start, const float* rand,
+                                              int64_t num_walks, int32_t walk_length, int64_t* n_out,
+                                              int64_t* e_out, uint32_t* status_flags, void* stream) {
+  walk_b200_csr g{};
+  g.rowptr = rowptr; g.col = col; g.num_nodes = num_nodes; g.num_edges = num_edges;
+  if (int rc = check_csr(&g)) return rc;
+  if (int rc = check_walk_sizes(num_walks, walk_length, start, n_out)) return rc;
+  if (num_walks > 0 && walk_length > 0 && !rand) return fail(WALK_B200_ERR_INVALID_ARG, "rand is NULL");
+  if (num_nodes > WALK_B200_NOALLOC_MAX_NODES)
+    return fail(WALK_B200_ERR_UNSUPPORTED,
+                "graph has %lld nodes; the built-in scratch of walk_b200_uniform_walk_noalloc holds %d "
+                "(use walk_b200_uniform_walk with caller-provided rowdesc, or rowdesc = NULL)",
+                (long long)num_nodes, WALK_B200_NOALLOC_MAX_NODES);
+  if ((uint64_t)num_edges > kDescStartMask)
+    return fail(WALK_B200_ERR_UNSUPPORTED, "graph has %lld edges; row descriptors address at most 2^36",
+                (long long)num_edges);
+  if (num_walks == 0) return WALK_B200_OK;
+  uint64_t* scratch = nullptr;
+  if (int rc = noalloc_scratch(&scratch)) return rc;
+  if (num_nodes > 0) {
+    // rewrites entries [0, num_nodes): whatever an earlier call left there is never read
+    rowdesc_pack_kernel<<<grid_for_streaming(num_nodes), kBlock, 0, (cudaStream_t)stream>>>(
+        rowptr, num_nodes, num_edges, scratch, status_flags);
+    if (int rc = check_launch("rowdesc_pack_kernel")) return rc;
+  }
+  UniformParams P{};
+  P.rowptr = rowptr; P.col = col; P.desc = num_nodes > 0 ? scratch : nullptr;
+  P.num_nodes = num_nodes; P.num_edges = num_edges;
+  P.start = start; P.rand = rand; P.num_walks = num_walks; P.walk_length = walk_length;
+  P.n_out = n_out; P.e_out = walk_length > 0 ? e_out : nullptr; P.flags = status_flags;
+  return launch_uniform(P, (cudaStream_t)stream);
+}
+
+// ======================================================================================
 // Resident graph + host-buffer entry points
 // ======================================================================================
 struct walk_b200_graph {
