@@ -228,14 +228,15 @@ def run_reference_arm(args, wl):
     return 0
 
 
-def workload_config(wl, n_nodes, n_edges, gpus):
+def workload_config(wl, n_nodes, n_edges, gpus, membership=None):
     c = {"workload": args_workload_name(wl), "graph": f"R-MAT scale {wl['scale']} edge factor {wl['edge_factor']} "
          f"(a,b,c,d)=(0.57,0.19,0.19,0.05) seed {wl['seed']}, symmetrised, deduplicated, no self-loops, int64 CSR",
          "num_nodes": n_nodes, "num_directed_edges": n_edges, "starts": "every node once", "walk_length": wl["L"],
          "sharding": f"start rows over {gpus} GPU(s), CSR replicated",
          "l2": "no flush between steps: col (8 B x edges) is far larger than the 126 MB L2"}
     if wl["kind"] == "node2vec":
-        c.update(p=wl["p"], q=wl["q"], draws="Philox4x32-10, key=seed, counter=(walk,step,attempt)")
+        c.update(p=wl["p"], q=wl["q"], draws="Philox4x32-10, key=seed, counter=(walk,step,attempt)",
+                 membership=membership)
     else:
         c.update(rand="float32 uniform [0,1) [n, walk_length], caller-supplied")
     return c
@@ -310,7 +311,10 @@ def run_ours(args, wl):
     b, e = shard_range(n_nodes, world, rank)
     rows = e - b
     start = torch.arange(b, e, dtype=torch.int64, device=dev)
-    graph = WalkGraph(rowptr, col, symmetric=True)
+    t_prep = time.perf_counter()
+    graph = WalkGraph(rowptr, col, symmetric=True, edgeset=(wl["kind"] == "node2vec" and args.membership == "hash"))
+    torch.cuda.synchronize(dev)
+    prep_s = time.perf_counter() - t_prep
     out = torch.empty((rows, L + 1), dtype=torch.int64, device=dev)
     stream = torch.cuda.current_stream(dev)
 
@@ -318,8 +322,15 @@ def run_ours(args, wl):
         # untimed instrumented pass: counts the 8-byte gathers this batch needs
         _, cnt = rejection_sampling(None, None, start, L, wl["p"], wl["q"], graph=graph, seed=PHILOX_SEED,
                                     walk_index_base=b, out=out, return_counters=True, check=True)
-        loads = cnt["loads"]
-        alg_bytes = 8 * loads + 8 * rows * (L + 1) + 8 * rows  # gathers + walk matrix + start
+        # algorithmic bytes of the reference's algorithm with a log-time membership test: per walk
+        # 16; first step 32 (24 if isolated); stay-in-place step 24; degree-1 step 32; sampled step
+        # 16 + 8 plus 8 per attempt plus, per membership test that can change the outcome,
+        # 16 + 8 * ceil(log2(deg(candidate) + 1))
+        alg_bytes = (16 * rows + 32 * cnt["steps_first"] + 24 * cnt["steps_deg0"] + 32 * cnt["steps_deg1"]
+                     + 24 * cnt["steps_sampled"] + 8 * cnt["attempts"] + 16 * cnt["membership"]
+                     + 8 * cnt["formula_probes"])
+        # what this implementation actually gathers and writes (8 B per gather issued)
+        gathered_bytes = 8 * cnt["loads"] + 8 * rows * (L + 1) + 8 * rows
         rand = None
 
         def step():
@@ -335,6 +346,7 @@ def run_ours(args, wl):
         stay = rows * L - moved
         # per step: row bounds 16 (8 via the packed descriptor, counted as the CSR's 16) + rand 4 + col 8 + out 8
         alg_bytes = rows * 16 + moved * 36 + stay * 24
+        gathered_bytes = rows * 16 + moved * 28 + stay * 12  # 8-byte descriptor instead of the 16-byte row pair
 
         def step():
             random_walk(None, None, start, rand, L, graph=graph, out=out)
@@ -350,10 +362,24 @@ def run_ours(args, wl):
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_source": f"of {peak_kind}", "traffic": None, "kernel": "node2vec_walk_kernel" if
                 wl["kind"] == "node2vec" else "uniform_walk_staged_kernel", "kernel_ms": kernel_ms,
-                "algorithmic_bytes_per_launch": alg_bytes,
+                "algorithmic_bytes_per_launch": alg_bytes, "gathered_bytes_per_launch": gathered_bytes,
+                "gathered_gbs": allsum(gathered_bytes / (kernel_ms * 1e-3) / 1e9) / world,
                 "algorithmic_bytes_per_walk_step": alg_bytes / max(1, rows * L)}
     if cnt:
         roofline["counters"] = cnt
+    # second ceiling: the device's rate of dependent random gathers that miss L2 (measured now)
+    if rank == 0 and not args.no_probe:
+        ceiling = _lib.gather_probe(2 << 30, 32)
+        if wl["kind"] == "node2vec":
+            # every row fetch, candidate gather and hash bucket is one random access (upper bound on DRAM misses)
+            accesses = cnt["steps_first"] + cnt["steps_deg1"] + cnt["steps_sampled"] + rows \
+                + cnt["attempts"] + cnt["steps_first"] + cnt["steps_deg1"] + cnt["probes"]
+        else:
+            accesses = 2 * moved + rows
+        roofline["random_access"] = {"ceiling_gathers_per_s": ceiling, "gathers_per_launch": int(accesses),
+                                     "achieved_gathers_per_s": accesses / (kernel_ms * 1e-3),
+                                     "frac": accesses / (kernel_ms * 1e-3) / ceiling,
+                                     "note": "gathers issued, an upper bound on DRAM-missing ones"}
 
     # ---- end to end: host buffers through the public API, copies inside the timed region
     e2e = None
@@ -364,7 +390,8 @@ def run_ours(args, wl):
         h_out = torch.empty((rows, L + 1), dtype=torch.int64, pin_memory=True)
         h_rand = rand.cpu().pin_memory() if rand is not None else None
         t_up = time.perf_counter()
-        hg = HostGraph(h_rowptr, h_col, symmetric=True, device=dev)
+        hg = HostGraph(h_rowptr, h_col, symmetric=True, device=dev,
+                       edgeset=(wl["kind"] == "node2vec" and args.membership == "hash"))
         upload_s = time.perf_counter() - t_up
         del graph, out
         torch.cuda.empty_cache()
@@ -410,8 +437,9 @@ def run_ours(args, wl):
             "metric": "walk_steps_per_sec", "value": value, "unit": "steps/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
-            "config": workload_config(wl, n_nodes, n_edges, world), "roofline": roofline, "cpu_baseline": cpu,
+            "config": workload_config(wl, n_nodes, n_edges, world, args.membership), "roofline": roofline, "cpu_baseline": cpu,
             "e2e": e2e, "gpu_launches": int(timed_launches), "clocks": clocks, "graph_build_s": build_s,
+            "graph_prepare_s_once": prep_s,
         }
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -429,6 +457,9 @@ def main():
     ap.add_argument("--workload", default="node2vec_rmat24", choices=list(WORKLOADS))
     ap.add_argument("--e2e-steps", type=int, default=3, help="end-to-end passes (each moves the whole walk matrix to the host)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target CPU time of the cpu_baseline sample")
+    ap.add_argument("--membership", default="hash", choices=["hash", "search"],
+                    help="node2vec membership test: edge hash set (built once per graph) or binary search over col")
+    ap.add_argument("--no-probe", action="store_true", help="skip the random-gather ceiling probe")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--tune", action="append", default=[], help="key=value passed to walk_b200_set_tuning")

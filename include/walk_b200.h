@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define WALK_B200_ABI_VERSION 1
+#define WALK_B200_ABI_VERSION 2
 
 /* ---- return codes ---- */
 #define WALK_B200_OK 0
@@ -48,12 +48,15 @@ extern "C" {
 #define WALK_B200_FLAG_DESC_OVERFLOW 0x10u /* a row start >= 2^36 or a degree >= 2^28: no packed descriptor */
 #define WALK_B200_FLAG_UNSORTED_ROW 0x20u /* csr_validate: a row is not strictly ascending */
 #define WALK_B200_FLAG_WAIT_TIMEOUT 0x40u /* reserved */
+#define WALK_B200_FLAG_EDGESET_FULL 0x80u /* edge hash set too small for the graph (build) or a probe chain ran away (lookup) */
 
 #define WALK_B200_MAX_ATTEMPTS (1u << 22)
 
 /* ---- graph description ---- */
 #define WALK_B200_CSR_SYMMETRIC 0x1u /* caller asserts (u,v) in E <=> (v,u) in E: lets node2vec search the previous
                                         node's row instead of the candidate's; results are identical on such graphs */
+
+#define WALK_B200_CSR_WANT_EDGESET 0x2u /* walk_b200_graph_create only: also build the edge hash set */
 
 typedef struct walk_b200_csr {
   const int64_t* rowptr;   /* device, [num_nodes + 1] */
@@ -63,6 +66,9 @@ typedef struct walk_b200_csr {
   const uint64_t* rowdesc; /* device, [num_nodes], from walk_b200_rowdesc_pack, or NULL (kernels then read rowptr) */
   uint32_t flags;          /* WALK_B200_CSR_* */
   uint32_t reserved;
+  const uint64_t* edgeset; /* device, [4 * edgeset_buckets], from walk_b200_edgeset_build, or NULL: node2vec then
+                              runs its membership test as a binary search over col */
+  uint64_t edgeset_buckets;
 } walk_b200_csr;
 
 /* node2vec instrumentation slots (device uint64[WALK_B200_COUNTER_COUNT], caller zeroes them) */
@@ -70,11 +76,13 @@ enum {
   WALK_B200_CNT_LOADS = 0,      /* 8-byte gathers issued (rowptr/rowdesc/col), all states */
   WALK_B200_CNT_ATTEMPTS,       /* candidate draws in the rejection loop (steps >= 1, degree >= 2) */
   WALK_B200_CNT_MEMBERSHIP,     /* membership tests actually run */
-  WALK_B200_CNT_PROBES,         /* binary-search probes of those tests */
+  WALK_B200_CNT_PROBES,         /* binary-search probes (or hash buckets read) of those tests */
   WALK_B200_CNT_STEPS_DEG0,
   WALK_B200_CNT_STEPS_DEG1,
   WALK_B200_CNT_STEPS_SAMPLED,
   WALK_B200_CNT_STEPS_FIRST,
+  WALK_B200_CNT_FORMULA_PROBES, /* sum over membership tests of ceil(log2(deg(candidate) + 1)): what a binary search
+                                   of the candidate's row, the reference's is_neighbor(x, t) done in log time, would probe */
   WALK_B200_COUNTER_COUNT
 };
 
@@ -122,6 +130,19 @@ int walk_b200_node2vec_walk(const walk_b200_csr* g, const int64_t* start, int64_
  */
 int walk_b200_rowdesc_pack(const int64_t* rowptr, int64_t num_nodes, int64_t num_edges,
                            uint64_t* rowdesc, uint32_t* status_flags, void* stream);
+
+/*
+ * Edge hash set: an exact set of all directed edges, so that node2vec's membership test
+ * "is t a neighbour of x" (is_neighbor, random_walks/BiasedRandomWalk.cpp:20-28, a linear
+ * scan there) costs about one 32-byte read instead of a binary search over col.
+ * walk_b200_edgeset_buckets gives the table size for a graph (16 bytes per edge: load
+ * factor 0.5); table is caller scratch of 32 * buckets bytes, 32-byte aligned. Needs
+ * num_nodes < 2^32 - 1 (else WALK_B200_ERR_UNSUPPORTED). Works for any CSR, directed or
+ * not, sorted or not. Put the pointer and bucket count into walk_b200_csr.
+ */
+int walk_b200_edgeset_buckets(int64_t num_edges, uint64_t* buckets);
+int walk_b200_edgeset_build(const walk_b200_csr* g, uint64_t* table, uint64_t buckets,
+                            uint32_t* status_flags, void* stream);
 
 /*
  * Full check the reference never makes (it reinterprets whatever it is given,
@@ -214,7 +235,16 @@ int walk_b200_uniform_walk_noalloc(const int64_t* rowptr, const int64_t* col, in
                                    int64_t num_walks, int32_t walk_length, int64_t* n_out,
                                    int64_t* e_out, uint32_t* status_flags, void* stream);
 
-/* Kernel variant selection for experiments ("uniform_chunk", "n2v_block", ...); unknown keys fail. */
+/*
+ * Device probe (diagnostic; allocates and frees array_bytes of device memory itself):
+ * the rate of dependent random 8-byte gathers over an array much larger than L2, one
+ * gather in flight per thread -- the access pattern of a walk step. On B200 this rate,
+ * not the byte bandwidth, bounds the walks: about 5e10 DRAM-missing gathers per second
+ * whether a miss moves 64 or 128 bytes. No counterpart in the reference.
+ */
+int walk_b200_gather_probe(size_t array_bytes, int32_t iters, double* gathers_per_second);
+
+/* Kernel variant selection for experiments ("uniform_variant", "n2v_member", "l2_hints", ...); unknown keys fail. */
 int walk_b200_set_tuning(const char* key, int32_t value);
 int walk_b200_get_tuning(const char* key, int32_t* value);
 

@@ -14,22 +14,22 @@ LIB_PATH = _PKG / "libwalk_b200.so"
 OK = 0
 ERR_INVALID_ARG, ERR_BAD_PQ, ERR_CUDA, ERR_CSR_INVALID, ERR_UNSUPPORTED, ERR_DEVICE_FLAGS = 1, 2, 3, 4, 5, 6
 FLAG_BAD_NODE, FLAG_BAD_EDGE, FLAG_ATTEMPT_CAP, FLAG_BAD_ROWPTR = 0x1, 0x2, 0x4, 0x8
-FLAG_DESC_OVERFLOW, FLAG_UNSORTED_ROW = 0x10, 0x20
-CSR_SYMMETRIC = 0x1
+FLAG_DESC_OVERFLOW, FLAG_UNSORTED_ROW, FLAG_EDGESET_FULL = 0x10, 0x20, 0x80
+CSR_SYMMETRIC, CSR_WANT_EDGESET = 0x1, 0x2
 COUNTER_NAMES = ("loads", "attempts", "membership", "probes",
-                 "steps_deg0", "steps_deg1", "steps_sampled", "steps_first")
+                 "steps_deg0", "steps_deg1", "steps_sampled", "steps_first", "formula_probes")
 
 # every symbol include/walk_b200.h declares
 EXPORTS = (
     "walk_b200_abi_version", "walk_b200_last_error", "walk_b200_launch_count",
     "walk_b200_uniform_walk", "walk_b200_node2vec_walk", "walk_b200_rowdesc_pack",
-    "walk_b200_csr_validate", "walk_b200_philox4x32_10", "walk_b200_node2vec_draw",
+    "walk_b200_csr_validate", "walk_b200_edgeset_buckets", "walk_b200_edgeset_build", "walk_b200_philox4x32_10", "walk_b200_node2vec_draw",
     "walk_b200_node2vec_thresholds", "walk_b200_shard_range",
     "walk_b200_graph_create", "walk_b200_graph_destroy", "walk_b200_graph_csr",
     "walk_b200_graph_device_bytes", "walk_b200_uniform_walk_host", "walk_b200_node2vec_walk_host",
     "walk_b200_l2_window_set", "walk_b200_l2_window_clear",
     "walk_b200_set_tuning", "walk_b200_get_tuning",
-    "walk_b200_uniform_walk_noalloc",
+    "walk_b200_uniform_walk_noalloc", "walk_b200_gather_probe",
 )
 NOALLOC_MAX_NODES = 1 << 20
 
@@ -37,7 +37,7 @@ NOALLOC_MAX_NODES = 1 << 20
 class Csr(C.Structure):
     _fields_ = [("rowptr", C.c_void_p), ("col", C.c_void_p), ("num_nodes", C.c_int64),
                 ("num_edges", C.c_int64), ("rowdesc", C.c_void_p), ("flags", C.c_uint32),
-                ("reserved", C.c_uint32)]
+                ("reserved", C.c_uint32), ("edgeset", C.c_void_p), ("edgeset_buckets", C.c_uint64)]
 
 
 class WalkError(RuntimeError):
@@ -66,6 +66,8 @@ def lib():
     L.walk_b200_node2vec_walk.argtypes = [C.POINTER(Csr), vp, i64, i32, dbl, dbl, u64, u64, vp, vp, vp, vp, vp]
     L.walk_b200_rowdesc_pack.argtypes = [vp, i64, i64, vp, vp, vp]
     L.walk_b200_csr_validate.argtypes = [C.POINTER(Csr), vp, i64, i32, vp, vp]
+    L.walk_b200_edgeset_buckets.argtypes = [i64, C.POINTER(u64)]
+    L.walk_b200_edgeset_build.argtypes = [C.POINTER(Csr), vp, u64, vp, vp]
     L.walk_b200_philox4x32_10.argtypes = [vp, vp, vp]
     L.walk_b200_philox4x32_10.restype = None
     L.walk_b200_node2vec_draw.argtypes = [u64, u64, u32, u32, C.POINTER(u32), C.POINTER(u32)]
@@ -81,6 +83,7 @@ def lib():
     L.walk_b200_l2_window_set.argtypes = [vp, C.c_size_t, C.c_float, vp, C.POINTER(C.c_size_t)]
     L.walk_b200_l2_window_clear.argtypes = [vp]
     L.walk_b200_uniform_walk_noalloc.argtypes = [vp, vp, i64, i64, vp, vp, i64, i32, vp, vp, vp, vp]
+    L.walk_b200_gather_probe.argtypes = [C.c_size_t, i32, C.POINTER(dbl)]
     L.walk_b200_set_tuning.argtypes = [C.c_char_p, i32]
     L.walk_b200_get_tuning.argtypes = [C.c_char_p, C.POINTER(i32)]
     for name in EXPORTS:  # AttributeError here = the built library is older than the header
@@ -128,6 +131,19 @@ def node2vec_thresholds(p: float, q: float):
     cuts = (C.c_uint32 * 3)()
     check(lib().walk_b200_node2vec_thresholds(p, q, C.byref(prob), C.byref(cuts)))
     return tuple(prob), tuple(cuts)
+
+
+def gather_probe(array_bytes: int = 2 << 30, iters: int = 32) -> float:
+    """Dependent random 8-byte gathers per second this device sustains out of DRAM."""
+    r = C.c_double(0.0)
+    check(lib().walk_b200_gather_probe(array_bytes, iters, C.byref(r)))
+    return float(r.value)
+
+
+def edgeset_buckets(num_edges: int) -> int:
+    b = C.c_uint64(0)
+    check(lib().walk_b200_edgeset_buckets(num_edges, C.byref(b)))
+    return int(b.value)
 
 
 def shard_range(num_walks: int, world_size: int, rank: int):

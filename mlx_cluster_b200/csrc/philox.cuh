@@ -18,17 +18,11 @@ __host__ __device__ __forceinline__ Philox4 philox4x32_10(uint32_t c0, uint32_t 
                                                           uint32_t c3, uint32_t k0, uint32_t k1) {
 #pragma unroll
   for (int r = 0; r < 10; r++) {
-#ifdef __CUDA_ARCH__
-    const uint32_t hi0 = __umulhi(kPhiloxM0, c0);
-    const uint32_t hi1 = __umulhi(kPhiloxM1, c2);
-    const uint32_t lo0 = kPhiloxM0 * c0;
-    const uint32_t lo1 = kPhiloxM1 * c2;
-#else
+    // one 32x32->64 multiply per product (a single wide multiply-add on the device)
     const uint64_t p0 = (uint64_t)kPhiloxM0 * c0;
     const uint64_t p1 = (uint64_t)kPhiloxM1 * c2;
     const uint32_t hi0 = (uint32_t)(p0 >> 32), lo0 = (uint32_t)p0;
     const uint32_t hi1 = (uint32_t)(p1 >> 32), lo1 = (uint32_t)p1;
-#endif
     const uint32_t n0 = hi1 ^ c1 ^ k0;
     const uint32_t n2 = hi0 ^ c3 ^ k1;
     c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;

@@ -51,8 +51,13 @@ int check_launch(const char* what) {
 
 // ---- tuning knobs (experiments; defaults are the measured best) ------------------
 struct Tuning {
-  std::atomic<int32_t> uniform_variant{0};  // 0 auto, 1 direct, 2 staged S=8, 3 staged S=16, 4 staged S=4
+  std::atomic<int32_t> uniform_variant{0};  // 0 auto, 1 direct, 2 staged S=8, 3 staged S=16, 4 staged S=4,
+                                            // 5 staged S=16 capped at 40 registers, 6 staged S=8 capped at 32
   std::atomic<int32_t> n2v_idx{0};          // 0 auto (32-bit indices when they fit), 1 force 64-bit
+  std::atomic<int32_t> n2v_member{0};       // 0 auto (hash set when the graph has one), 1 ignore the hash set
+  std::atomic<int32_t> n2v_blocks_per_sm{0};  // 0 = what the occupancy calculator allows
+  std::atomic<int32_t> l2_hints{3};         // bit 0: evict-last row bounds, bit 1: evict-first streams
+  std::atomic<int32_t> l2_fetch_granularity{0};  // set only through walk_b200_set_tuning (applies the CUDA limit)
   std::atomic<int32_t> host_slab_mb{256};   // walk-matrix bytes per pipeline slab of the host entry points
   std::atomic<int32_t> use_rowdesc{1};      // host entry points: build and use the packed row descriptor
 } g_tuning;
@@ -61,6 +66,10 @@ std::atomic<int32_t>* tuning_slot(const char* key) {
   if (!key) return nullptr;
   if (!strcmp(key, "uniform_variant")) return &g_tuning.uniform_variant;
   if (!strcmp(key, "n2v_idx")) return &g_tuning.n2v_idx;
+  if (!strcmp(key, "n2v_member")) return &g_tuning.n2v_member;
+  if (!strcmp(key, "n2v_blocks_per_sm")) return &g_tuning.n2v_blocks_per_sm;
+  if (!strcmp(key, "l2_hints")) return &g_tuning.l2_hints;
+  if (!strcmp(key, "l2_fetch_granularity")) return &g_tuning.l2_fetch_granularity;
   if (!strcmp(key, "host_slab_mb")) return &g_tuning.host_slab_mb;
   if (!strcmp(key, "use_rowdesc")) return &g_tuning.use_rowdesc;
   return nullptr;
@@ -123,22 +132,37 @@ int thresholds(double p, double q, double prob[3], uint32_t cuts[3]) {
 template <bool USE_DESC, bool HAS_EOUT>
 int launch_uniform_t(const UniformParams& P, cudaStream_t s) {
   int variant = g_tuning.uniform_variant.load();
-  if (variant == 0) variant = P.walk_length >= 4 ? 2 : 1;
-  const int64_t n = P.num_walks;
+  if (variant == 0) variant = P.walk_length >= 4 ? 7 : 1;
+  const unsigned grid = (unsigned)blocks_for(P.num_walks);
   switch (variant) {
     case 1:
-      uniform_walk_direct_kernel<USE_DESC, HAS_EOUT><<<(unsigned)blocks_for(n), kBlock, 0, s>>>(P);
+      uniform_walk_direct_kernel<USE_DESC, HAS_EOUT><<<grid, kBlock, 0, s>>>(P);
       return check_launch("uniform_walk_direct_kernel");
-    case 3:
-      uniform_walk_staged_kernel<16, USE_DESC, HAS_EOUT><<<(unsigned)blocks_for(n), kBlock, 0, s>>>(P);
-      return check_launch("uniform_walk_staged_kernel<16>");
-    case 4:
-      uniform_walk_staged_kernel<4, USE_DESC, HAS_EOUT><<<(unsigned)blocks_for(n), kBlock, 0, s>>>(P);
-      return check_launch("uniform_walk_staged_kernel<4>");
     case 2:
-    default:
-      uniform_walk_staged_kernel<8, USE_DESC, HAS_EOUT><<<(unsigned)blocks_for(n), kBlock, 0, s>>>(P);
+      uniform_walk_staged_kernel<8, 1, USE_DESC, HAS_EOUT><<<grid, kBlock, 0, s>>>(P);
       return check_launch("uniform_walk_staged_kernel<8>");
+    case 4:
+      uniform_walk_staged_kernel<4, 1, USE_DESC, HAS_EOUT><<<grid, kBlock, 0, s>>>(P);
+      return check_launch("uniform_walk_staged_kernel<4>");
+    case 5:
+      uniform_walk_staged_kernel<16, 6, USE_DESC, HAS_EOUT><<<grid, kBlock, 0, s>>>(P);
+      return check_launch("uniform_walk_staged_kernel<16,6>");
+    case 6:
+      uniform_walk_staged_kernel<8, 8, USE_DESC, HAS_EOUT><<<grid, kBlock, 0, s>>>(P);
+      return check_launch("uniform_walk_staged_kernel<8,8>");
+    case 7:
+      uniform_walk_staged_kernel<16, 4, USE_DESC, HAS_EOUT><<<grid, kBlock, 0, s>>>(P);
+      return check_launch("uniform_walk_staged_kernel<16,4>");
+    case 8:
+      uniform_walk_staged_kernel<16, 5, USE_DESC, HAS_EOUT><<<grid, kBlock, 0, s>>>(P);
+      return check_launch("uniform_walk_staged_kernel<16,5>");
+    case 9:
+      uniform_walk_staged_kernel<8, 6, USE_DESC, HAS_EOUT><<<grid, kBlock, 0, s>>>(P);
+      return check_launch("uniform_walk_staged_kernel<8,6>");
+    case 3:
+    default:
+      uniform_walk_staged_kernel<16, 1, USE_DESC, HAS_EOUT><<<grid, kBlock, 0, s>>>(P);
+      return check_launch("uniform_walk_staged_kernel<16>");
   }
 }
 
@@ -148,31 +172,96 @@ int launch_uniform(const UniformParams& P, cudaStream_t s) {
   return e ? launch_uniform_t<false, true>(P, s) : launch_uniform_t<false, false>(P, s);
 }
 
-template <typename idx_t, bool SYM, bool USE_DESC>
-int launch_n2v_t(const Node2vecParams& P, cudaStream_t s) {
-  const unsigned grid = (unsigned)blocks_for(P.num_walks);
-  const bool e = P.e_out != nullptr, c = P.counters != nullptr;
-  if (c) {
-    if (e) node2vec_walk_kernel<idx_t, SYM, USE_DESC, true, true><<<grid, kBlock, 0, s>>>(P);
-    else node2vec_walk_kernel<idx_t, SYM, USE_DESC, false, true><<<grid, kBlock, 0, s>>>(P);
-  } else {
-    if (e) node2vec_walk_kernel<idx_t, SYM, USE_DESC, true, false><<<grid, kBlock, 0, s>>>(P);
-    else node2vec_walk_kernel<idx_t, SYM, USE_DESC, false, false><<<grid, kBlock, 0, s>>>(P);
+int sm_count() {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int v = cached[dev].load();
+  if (v == 0) {
+    if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+    cached[dev].store(v);
   }
+  return v;
+}
+
+// Launch-wide chunk counters of the node2vec kernel. Each launch takes the next slot of
+// this ring, clears it on its stream and hands it to the kernel. The ring lives in the
+// library's device image, so a launch allocates nothing. A slot is reused after
+// kQueueSlots further launches on the same device: more node2vec launches than that in
+// flight at once (across streams) are not supported.
+constexpr int kQueueSlots = 4096;
+__device__ unsigned long long g_queue_slots[kQueueSlots];
+std::mutex g_queue_mu;
+unsigned long long* g_queue_base[64] = {};
+std::atomic<uint32_t> g_queue_next{0};
+
+int next_queue_slot(unsigned long long** out) {
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(WALK_B200_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  {
+    std::lock_guard<std::mutex> lock(g_queue_mu);
+    if (!g_queue_base[dev]) {
+      void* p = nullptr;
+      CUDA_TRY(cudaGetSymbolAddress(&p, g_queue_slots));
+      g_queue_base[dev] = static_cast<unsigned long long*>(p);
+    }
+  }
+  *out = g_queue_base[dev] + (g_queue_next.fetch_add(1) % kQueueSlots);
+  return WALK_B200_OK;
+}
+
+// Persistent launch: as many blocks as fit on the device at once (or fewer, if the batch is small).
+template <typename K>
+int launch_n2v_kernel(K kernel, const Node2vecParams& P0, cudaStream_t s) {
+  Node2vecParams P = P0;
+  if (int rc = next_queue_slot(&P.queue)) return rc;
+  CUDA_TRY(cudaMemsetAsync(P.queue, 0, sizeof(unsigned long long), s));
+  int per_sm = g_tuning.n2v_blocks_per_sm.load();
+  if (per_sm <= 0) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kBlock, 0) != cudaSuccess || per_sm <= 0) {
+      (void)cudaGetLastError();
+      per_sm = 4;
+    }
+  }
+  int64_t grid = (int64_t)sm_count() * per_sm;
+  const int64_t needed = (P.num_walks + kBlock - 1) / kBlock;  // one chunk of 32 walks per warp at least
+  if (grid > needed) grid = needed;
+  if (grid < 1) grid = 1;
+  kernel<<<(unsigned)grid, kBlock, 0, s>>>(P);
   return check_launch("node2vec_walk_kernel");
 }
 
+template <typename idx_t, int MEMBER, bool USE_DESC>
+int launch_n2v_t(const Node2vecParams& P, cudaStream_t s) {
+  const bool e = P.e_out != nullptr, c = P.counters != nullptr;
+  if (c) {
+    if (e) return launch_n2v_kernel(node2vec_walk_kernel<idx_t, MEMBER, USE_DESC, true, true>, P, s);
+    return launch_n2v_kernel(node2vec_walk_kernel<idx_t, MEMBER, USE_DESC, false, true>, P, s);
+  }
+  if (e) return launch_n2v_kernel(node2vec_walk_kernel<idx_t, MEMBER, USE_DESC, true, false>, P, s);
+  return launch_n2v_kernel(node2vec_walk_kernel<idx_t, MEMBER, USE_DESC, false, false>, P, s);
+}
+
 template <typename idx_t>
-int launch_n2v_i(const Node2vecParams& P, bool sym, cudaStream_t s) {
+int launch_n2v_i(const Node2vecParams& P, int member, cudaStream_t s) {
   const bool d = P.desc != nullptr;
-  if (sym) return d ? launch_n2v_t<idx_t, true, true>(P, s) : launch_n2v_t<idx_t, true, false>(P, s);
-  return d ? launch_n2v_t<idx_t, false, true>(P, s) : launch_n2v_t<idx_t, false, false>(P, s);
+  switch (member) {
+    case MEMBER_HASH:
+      return d ? launch_n2v_t<idx_t, MEMBER_HASH, true>(P, s) : launch_n2v_t<idx_t, MEMBER_HASH, false>(P, s);
+    case MEMBER_SEARCH_PREV:
+      return d ? launch_n2v_t<idx_t, MEMBER_SEARCH_PREV, true>(P, s) : launch_n2v_t<idx_t, MEMBER_SEARCH_PREV, false>(P, s);
+    default:
+      return d ? launch_n2v_t<idx_t, MEMBER_SEARCH_CAND, true>(P, s) : launch_n2v_t<idx_t, MEMBER_SEARCH_CAND, false>(P, s);
+  }
 }
 
 int launch_n2v(const Node2vecParams& P, bool sym, cudaStream_t s) {
+  int member = sym ? MEMBER_SEARCH_PREV : MEMBER_SEARCH_CAND;
+  if (P.edgeset && P.edgeset_buckets > 0 && g_tuning.n2v_member.load() != 1) member = MEMBER_HASH;
   const bool fits32 = P.num_nodes <= 0x7fffffffll && P.num_edges <= 0xffffffffll;
-  if (fits32 && g_tuning.n2v_idx.load() != 1) return launch_n2v_i<uint32_t>(P, sym, s);
-  return launch_n2v_i<int64_t>(P, sym, s);
+  if (fits32 && g_tuning.n2v_idx.load() != 1) return launch_n2v_i<uint32_t>(P, member, s);
+  return launch_n2v_i<int64_t>(P, member, s);
 }
 
 int grid_for_streaming(int64_t n) {
@@ -199,6 +288,12 @@ uint64_t walk_b200_launch_count(void) { return g_launches.load(); }
 int walk_b200_set_tuning(const char* key, int32_t value) {
   auto* slot = tuning_slot(key);
   if (!slot) return fail(WALK_B200_ERR_INVALID_ARG, "unknown tuning key '%s'", key ? key : "(null)");
+  if (slot == &g_tuning.l2_fetch_granularity) {
+    // per-context hint to the L2 on how much to fetch from DRAM per miss (32, 64 or 128 bytes)
+    if (value != 32 && value != 64 && value != 128)
+      return fail(WALK_B200_ERR_INVALID_ARG, "l2_fetch_granularity must be 32, 64 or 128");
+    CUDA_TRY(cudaDeviceSetLimit(cudaLimitMaxL2FetchGranularity, (size_t)value));
+  }
   slot->store(value);
   return WALK_B200_OK;
 }
@@ -260,6 +355,7 @@ int walk_b200_uniform_walk(const walk_b200_csr* g, const int64_t* start, const f
   P.num_nodes = g->num_nodes; P.num_edges = g->num_edges;
   P.start = start; P.rand = rand; P.num_walks = num_walks; P.walk_length = walk_length;
   P.n_out = n_out; P.e_out = walk_length > 0 ? e_out : nullptr; P.flags = status_flags;
+  P.hints = g_tuning.l2_hints.load();
   return launch_uniform(P, (cudaStream_t)stream);
 }
 
@@ -283,6 +379,14 @@ int walk_b200_node2vec_walk(const walk_b200_csr* g, const int64_t* start, int64_
   P.max_attempts = WALK_B200_MAX_ATTEMPTS;
   P.n_out = n_out; P.e_out = walk_length > 0 ? e_out : nullptr;
   P.flags = status_flags; P.counters = (unsigned long long*)counters;
+  P.hints = g_tuning.l2_hints.load();
+  if (g->edgeset && g->edgeset_buckets > 0) {
+    if (g->num_nodes >= 0xffffffffll)
+      return fail(WALK_B200_ERR_UNSUPPORTED, "the edge hash set needs num_nodes < 2^32 - 1");
+    if ((reinterpret_cast<uintptr_t>(g->edgeset) & 31) != 0)
+      return fail(WALK_B200_ERR_INVALID_ARG, "edgeset must be 32-byte aligned");
+    P.edgeset = g->edgeset; P.edgeset_buckets = g->edgeset_buckets;
+  }
   return launch_n2v(P, (g->flags & WALK_B200_CSR_SYMMETRIC) != 0, (cudaStream_t)stream);
 }
 
@@ -296,6 +400,32 @@ int walk_b200_rowdesc_pack(const int64_t* rowptr, int64_t num_nodes, int64_t num
   return check_launch("rowdesc_pack_kernel");
 }
 
+int walk_b200_edgeset_buckets(int64_t num_edges, uint64_t* buckets) {
+  if (num_edges < 0 || !buckets) return fail(WALK_B200_ERR_INVALID_ARG, "bad edge count or NULL result");
+  // load factor 0.5: two slots per edge, four slots per bucket; never empty
+  uint64_t b = ((uint64_t)num_edges * 2 + kEdgeSlotsPerBucket - 1) / kEdgeSlotsPerBucket;
+  *buckets = b < 64 ? 64 : b;
+  return WALK_B200_OK;
+}
+
+int walk_b200_edgeset_build(const walk_b200_csr* g, uint64_t* table, uint64_t buckets,
+                            uint32_t* status_flags, void* stream) {
+  if (int rc = check_csr(g)) return rc;
+  if (!table || buckets == 0) return fail(WALK_B200_ERR_INVALID_ARG, "edge set table is NULL or empty");
+  if ((reinterpret_cast<uintptr_t>(table) & 31) != 0)
+    return fail(WALK_B200_ERR_INVALID_ARG, "edge set table must be 32-byte aligned");
+  if (g->num_nodes >= 0xffffffffll)
+    return fail(WALK_B200_ERR_UNSUPPORTED, "the edge hash set needs num_nodes < 2^32 - 1");
+  if (buckets * kEdgeSlotsPerBucket < (uint64_t)g->num_edges + (uint64_t)g->num_edges / 4)
+    return fail(WALK_B200_ERR_INVALID_ARG, "edge set table too small: %llu buckets for %lld edges",
+                (unsigned long long)buckets, (long long)g->num_edges);
+  CUDA_TRY(cudaMemsetAsync(table, 0xff, buckets * kEdgeSlotsPerBucket * sizeof(uint64_t), (cudaStream_t)stream));
+  if (g->num_edges == 0) return WALK_B200_OK;
+  edgeset_build_kernel<<<grid_for_streaming(g->num_edges), kBlock, 0, (cudaStream_t)stream>>>(
+      g->rowptr, g->col, g->num_nodes, g->num_edges, (unsigned long long*)table, buckets, status_flags);
+  return check_launch("edgeset_build_kernel");
+}
+
 int walk_b200_csr_validate(const walk_b200_csr* g, const int64_t* start, int64_t num_walks,
                            int32_t check_sorted, uint32_t* status_flags, void* stream) {
   if (int rc = check_csr(g)) return rc;
@@ -307,6 +437,52 @@ int walk_b200_csr_validate(const walk_b200_csr* g, const int64_t* start, int64_t
   csr_validate_kernel<<<grid_for_streaming(work), kBlock, 0, (cudaStream_t)stream>>>(
       g->rowptr, g->col, g->num_nodes, g->num_edges, start, start ? num_walks : 0, check_sorted, status_flags);
   return check_launch("csr_validate_kernel");
+}
+
+// ---- device probe -------------------------------------------------------------------
+int walk_b200_gather_probe(size_t array_bytes, int32_t iters, double* gathers_per_second) {
+  if (!gathers_per_second || iters < 1 || array_bytes < (1u << 20))
+    return fail(WALK_B200_ERR_INVALID_ARG, "gather probe needs an array of at least 1 MiB and iters >= 1");
+  *gathers_per_second = 0.0;
+  int64_t* data = nullptr;
+  int64_t* sink = nullptr;
+  cudaEvent_t a = nullptr, b = nullptr;
+  const uint64_t n = array_bytes / 8;
+  const int threads = 1 << 22;
+  int rc = WALK_B200_OK;
+  auto cleanup = [&]() {
+    if (a) cudaEventDestroy(a);
+    if (b) cudaEventDestroy(b);
+    if (data) cudaFree(data);
+    if (sink) cudaFree(sink);
+  };
+#define P_TRY(expr)                                                                                    \
+  do {                                                                                                 \
+    cudaError_t err__ = (expr);                                                                        \
+    if (err__ != cudaSuccess) {                                                                        \
+      rc = fail(WALK_B200_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(err__));                \
+      cleanup();                                                                                       \
+      return rc;                                                                                       \
+    }                                                                                                  \
+  } while (0)
+  P_TRY(cudaMalloc((void**)&data, n * 8));
+  P_TRY(cudaMalloc((void**)&sink, 8));
+  P_TRY(cudaMemset(data, 0, n * 8));
+  P_TRY(cudaEventCreate(&a));
+  P_TRY(cudaEventCreate(&b));
+  gather_probe_kernel<<<threads / kBlock, kBlock>>>(data, n, iters, sink);  // warm-up
+  if ((rc = check_launch("gather_probe_kernel"))) { cleanup(); return rc; }
+  P_TRY(cudaEventRecord(a));
+  gather_probe_kernel<<<threads / kBlock, kBlock>>>(data, n, iters, sink);
+  if ((rc = check_launch("gather_probe_kernel"))) { cleanup(); return rc; }
+  P_TRY(cudaEventRecord(b));
+  P_TRY(cudaEventSynchronize(b));
+  float ms = 0.f;
+  P_TRY(cudaEventElapsedTime(&ms, a, b));
+#undef P_TRY
+  cleanup();
+  if (ms > 0.f) *gathers_per_second = (double)threads * iters / (ms * 1e-3);
+  return WALK_B200_OK;
 }
 
 // ---- L2 residency hint -------------------------------------------------------------
@@ -418,6 +594,7 @@ extern "C" int walk_b200_uniform_walk_noalloc(const int64_t* rowptr, const int64
   P.num_nodes = num_nodes; P.num_edges = num_edges;
   P.start = start; P.rand = rand; P.num_walks = num_walks; P.walk_length = walk_length;
   P.n_out = n_out; P.e_out = walk_length > 0 ? e_out : nullptr; P.flags = status_flags;
+  P.hints = g_tuning.l2_hints.load();
   return launch_uniform(P, (cudaStream_t)stream);
 }
 
@@ -431,6 +608,8 @@ struct walk_b200_graph {
   int64_t* d_rowptr = nullptr;
   int64_t* d_col = nullptr;
   uint64_t* d_desc = nullptr;
+  uint64_t* d_edgeset = nullptr;
+  uint64_t edgeset_buckets = 0;
   uint32_t* d_flags = nullptr;
   static constexpr int kLanes = 3;  // slabs in flight: copy-in, kernel, copy-out
   cudaStream_t streams[kLanes] = {};
@@ -471,13 +650,14 @@ int grow(T** bufs, size_t* cap, size_t need) {
 int flags_to_status(uint32_t f) {
   if (!f) return WALK_B200_OK;
   return fail(WALK_B200_ERR_DEVICE_FLAGS,
-              "kernel raised status flags 0x%x:%s%s%s%s%s%s", f,
+              "kernel raised status flags 0x%x:%s%s%s%s%s%s%s", f,
               (f & WALK_B200_FLAG_BAD_NODE) ? " node id out of range;" : "",
               (f & WALK_B200_FLAG_BAD_EDGE) ? " edge index out of range (rand outside [0,1)?);" : "",
               (f & WALK_B200_FLAG_ATTEMPT_CAP) ? " rejection attempt cap hit;" : "",
               (f & WALK_B200_FLAG_BAD_ROWPTR) ? " rowptr malformed;" : "",
               (f & WALK_B200_FLAG_DESC_OVERFLOW) ? " row descriptor overflow;" : "",
-              (f & WALK_B200_FLAG_UNSORTED_ROW) ? " row not strictly ascending;" : "");
+              (f & WALK_B200_FLAG_UNSORTED_ROW) ? " row not strictly ascending;" : "",
+              (f & WALK_B200_FLAG_EDGESET_FULL) ? " edge hash set overflow;" : "");
 }
 
 // Runs one walk over host buffers in slabs: H2D(start[, rand]) -> kernel -> D2H(walks)
@@ -514,6 +694,7 @@ int run_host_walk(walk_b200_graph* g, bool biased, const int64_t* h_start, const
   walk_b200_csr csr{};
   csr.rowptr = g->d_rowptr; csr.col = g->d_col; csr.num_nodes = g->num_nodes; csr.num_edges = g->num_edges;
   csr.rowdesc = g->d_desc; csr.flags = g->csr_flags;
+  csr.edgeset = g->d_edgeset; csr.edgeset_buckets = g->edgeset_buckets;
 
   int lane = 0;
   for (int64_t r0 = 0; r0 < n; r0 += slab_rows, lane = (lane + 1) % walk_b200_graph::kLanes) {
@@ -590,6 +771,16 @@ int walk_b200_graph_create(const int64_t* h_rowptr, const int64_t* h_col, int64_
       g->d_desc = nullptr;
     }
   }
+  if ((csr_flags & WALK_B200_CSR_WANT_EDGESET) && num_edges > 0 && num_nodes < 0xffffffffll) {
+    walk_b200_csr csr{};
+    csr.rowptr = g->d_rowptr; csr.col = g->d_col; csr.num_nodes = num_nodes; csr.num_edges = num_edges;
+    if (int rc = walk_b200_edgeset_buckets(num_edges, &g->edgeset_buckets)) return bail(rc);
+    G_TRY(cudaMalloc((void**)&g->d_edgeset, g->edgeset_buckets * kEdgeSlotsPerBucket * sizeof(uint64_t)));
+    if (int rc = walk_b200_edgeset_build(&csr, g->d_edgeset, g->edgeset_buckets, g->d_flags, s)) return bail(rc);
+    G_TRY(cudaMemcpyAsync(&f, g->d_flags, 4, cudaMemcpyDeviceToHost, s));
+    G_TRY(cudaStreamSynchronize(s));
+    if (f) { flags_to_status(f); return bail(fail(WALK_B200_ERR_CSR_INVALID, "edge set build failed: %s", std::string(g_last_error).c_str())); }
+  }
   G_TRY(cudaStreamSynchronize(s));
 #undef G_TRY
   *out = g;
@@ -610,6 +801,7 @@ int walk_b200_graph_destroy(walk_b200_graph* g) {
     if (g->d_rowptr) cudaFree(g->d_rowptr);
     if (g->d_col) cudaFree(g->d_col);
     if (g->d_desc) cudaFree(g->d_desc);
+    if (g->d_edgeset) cudaFree(g->d_edgeset);
     if (g->d_flags) cudaFree(g->d_flags);
   }
   delete g;
@@ -621,12 +813,14 @@ int walk_b200_graph_csr(const walk_b200_graph* g, walk_b200_csr* out) {
   memset(out, 0, sizeof(*out));
   out->rowptr = g->d_rowptr; out->col = g->d_col; out->num_nodes = g->num_nodes; out->num_edges = g->num_edges;
   out->rowdesc = g->d_desc; out->flags = g->csr_flags;
+  out->edgeset = g->d_edgeset; out->edgeset_buckets = g->edgeset_buckets;
   return WALK_B200_OK;
 }
 
 int walk_b200_graph_device_bytes(const walk_b200_graph* g, int64_t* bytes) {
   if (!g || !bytes) return fail(WALK_B200_ERR_INVALID_ARG, "graph or bytes is NULL");
-  *bytes = (g->num_nodes + 1) * 8 + g->num_edges * 8 + (g->d_desc ? g->num_nodes * 8 : 0);
+  *bytes = (g->num_nodes + 1) * 8 + g->num_edges * 8 + (g->d_desc ? g->num_nodes * 8 : 0) +
+           (int64_t)(g->d_edgeset ? g->edgeset_buckets * kEdgeSlotsPerBucket * 8 : 0);
   return WALK_B200_OK;
 }
 

@@ -15,6 +15,7 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <cstdint>
+#include <type_traits>
 
 #include "../../include/walk_b200.h"
 #include "philox.cuh"
@@ -31,21 +32,89 @@ __device__ __forceinline__ void raise_flag(uint32_t* flags, uint32_t bit) {
   if (flags) atomicOr(flags, bit);
 }
 
+// ---- L2 eviction policies ---------------------------------------------------------
+// Row bounds are re-read all the time (accesses are skewed to hub nodes) while col
+// gathers, rand and the walk matrix stream through once: the former are loaded with an
+// evict-last policy, the latter with evict-first, so that the stream does not flush the
+// row descriptors out of L2. `hints` bit 0 enables the former, bit 1 the latter.
+struct L2Policy {
+  uint64_t keep, stream, normal;
+};
+
+__device__ __forceinline__ L2Policy make_policies(int hints) {
+  L2Policy p;
+  asm("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p.normal));
+  p.keep = p.normal;
+  p.stream = p.normal;
+  if (hints & 1) asm("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p.keep));
+  if (hints & 2) asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p.stream));
+  return p;
+}
+
+// Read-only 8-byte random gather with an L2 policy (inputs never change during a launch).
+// On this part a missing gather pulls a whole 128-byte line from DRAM by default; the
+// 64-byte prefetch size halves that (measured: 123 -> 63 bytes of DRAM per gather).
+__device__ __forceinline__ int64_t ld8(const void* addr, uint64_t policy) {
+  int64_t v;
+  asm("ld.global.nc.L2::cache_hint.L2::64B.b64 %0, [%1], %2;" : "=l"(v) : "l"(addr), "l"(policy));
+  return v;
+}
+__device__ __forceinline__ uint32_t ld4(const void* addr, uint64_t policy) {
+  uint32_t v;
+  asm("ld.global.nc.L2::cache_hint.b32 %0, [%1], %2;" : "=r"(v) : "l"(addr), "l"(policy));
+  return v;
+}
+__device__ __forceinline__ ulonglong2 ld16(const void* addr, uint64_t policy) {
+  ulonglong2 v;
+  asm("ld.global.nc.L2::cache_hint.L2::64B.v2.b64 {%0, %1}, [%2], %3;" : "=l"(v.x), "=l"(v.y) : "l"(addr), "l"(policy));
+  return v;
+}
+__device__ __forceinline__ void st8(void* addr, int64_t v, uint64_t policy) {
+  asm volatile("st.global.L2::cache_hint.b64 [%0], %1, %2;" ::"l"(addr), "l"(v), "l"(policy) : "memory");
+}
+
 // Row bounds of node v: one 8-byte load when a packed descriptor exists.
 template <bool USE_DESC>
 __device__ __forceinline__ void load_row(const int64_t* __restrict__ rowptr,
                                          const uint64_t* __restrict__ desc, int64_t v,
-                                         int64_t& row_start, int64_t& deg) {
+                                         uint64_t policy, int64_t& row_start, int64_t& deg) {
   if (USE_DESC) {
-    const uint64_t d = __ldg(desc + v);
+    const uint64_t d = (uint64_t)ld8(desc + v, policy);
     row_start = (int64_t)(d & kDescStartMask);
     deg = (int64_t)(d >> kDescStartBits);
   } else {
-    const int64_t a = __ldg(rowptr + v);
-    const int64_t b = __ldg(rowptr + v + 1);
+    const int64_t a = ld8(rowptr + v, policy);
+    const int64_t b = ld8(rowptr + v + 1, policy);
     row_start = a;
     deg = b - a;
   }
+}
+
+// ---------------------------------------------------------------------------------
+// gather_probe: what this device sustains in dependent random 8-byte gathers that miss L2.
+// Each thread chases a pseudo-random chain through a large array, one gather in flight
+// per thread, exactly the access pattern of a walk step. The walks cannot beat this rate
+// per DRAM-missing gather, whatever their byte counts say.
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t splitmix64(uint64_t z) {
+  z ^= z >> 30; z *= 0xbf58476d1ce4e5b9ull;
+  z ^= z >> 27; z *= 0x94d049bb133111ebull;
+  z ^= z >> 31;
+  return z;
+}
+
+__global__ void __launch_bounds__(kBlock) gather_probe_kernel(const int64_t* __restrict__ data,
+                                                              uint64_t num_elems, int iters,
+                                                              int64_t* sink) {
+  const L2Policy pol = make_policies(0);
+  const uint64_t tid = (uint64_t)blockIdx.x * kBlock + threadIdx.x;
+  uint64_t idx = splitmix64(tid + 1);
+  int64_t acc = 0;
+  for (int i = 0; i < iters; i++) {
+    idx = splitmix64(idx + (uint64_t)acc);
+    acc += ld8(data + __umul64hi(idx, num_elems), pol.normal);
+  }
+  if (acc == 0x7fffffffffffffffll) *sink = acc;  // never true on a zeroed array; keeps the chain alive
 }
 
 // ---------------------------------------------------------------------------------
@@ -121,6 +190,7 @@ struct UniformParams {
   const float* rand;
   int64_t num_walks;
   int32_t walk_length;
+  int32_t hints;
   int64_t* n_out;
   int64_t* e_out;
   uint32_t* flags;
@@ -128,12 +198,15 @@ struct UniformParams {
 
 // One uniform step from `cur` with draw r. Same float32 arithmetic as the reference:
 // degree converted to float32 (round to nearest), float32 product, truncation.
+// A node without out-edges parks the walk for good (its row can never gain an edge).
 template <bool USE_DESC>
-__device__ __forceinline__ int64_t uniform_step(const UniformParams& P, int64_t& cur, float r) {
+__device__ __forceinline__ int64_t uniform_step(const UniformParams& P, const L2Policy& pol, int64_t& cur,
+                                                bool& parked, float r) {
   int64_t rs, deg;
-  load_row<USE_DESC>(P.rowptr, P.desc, cur, rs, deg);
+  load_row<USE_DESC>(P.rowptr, P.desc, cur, pol.keep, rs, deg);
   if (deg <= 0) {
     if (deg < 0) raise_flag(P.flags, WALK_B200_FLAG_BAD_ROWPTR);
+    parked = true;
     return -1;
   }
   const float prod = __fmul_rn(r, __ll2float_rn(deg));
@@ -142,9 +215,10 @@ __device__ __forceinline__ int64_t uniform_step(const UniformParams& P, int64_t&
     raise_flag(P.flags, WALK_B200_FLAG_BAD_EDGE);
     e = e < 0 ? 0 : P.num_edges - 1;
   }
-  const int64_t nxt = __ldg(P.col + e);
+  const int64_t nxt = ld8(P.col + e, pol.stream);
   if ((uint64_t)nxt >= (uint64_t)P.num_nodes) {
     raise_flag(P.flags, WALK_B200_FLAG_BAD_NODE);  // park: keep cur
+    parked = true;
   } else {
     cur = nxt;
   }
@@ -158,6 +232,7 @@ template <bool USE_DESC, bool HAS_EOUT>
 __global__ void __launch_bounds__(kBlock) uniform_walk_direct_kernel(const UniformParams P) {
   const int64_t w = (int64_t)blockIdx.x * kBlock + threadIdx.x;
   if (w >= P.num_walks) return;
+  const L2Policy pol = make_policies(P.hints);
   const int64_t L = P.walk_length;
   int64_t cur = P.start[w];
   int64_t* out = P.n_out + w * (L + 1);
@@ -169,7 +244,7 @@ __global__ void __launch_bounds__(kBlock) uniform_walk_direct_kernel(const Unifo
   }
   for (int64_t l = 0; l < L; l++) {
     int64_t e = -1;
-    if (!parked) e = uniform_step<USE_DESC>(P, cur, __ldg(P.rand + w * L + l));
+    if (!parked) e = uniform_step<USE_DESC>(P, pol, cur, parked, __ldg(P.rand + w * L + l));
     out[l + 1] = cur;
     if (HAS_EOUT) P.e_out[w * L + l] = e;
   }
@@ -183,8 +258,8 @@ __global__ void __launch_bounds__(kBlock) uniform_walk_direct_kernel(const Unifo
 // segments of S consecutive int64. Global traffic on both sides is whole sectors; the
 // only divergent accesses left per step are the row fetch and the col gather. The next
 // chunk's rand is prefetched into registers while the current chunk walks.
-template <int S, bool USE_DESC, bool HAS_EOUT>
-__global__ void __launch_bounds__(kBlock) uniform_walk_staged_kernel(const UniformParams P) {
+template <int S, int MIN_BLOCKS, bool USE_DESC, bool HAS_EOUT>
+__global__ void __launch_bounds__(kBlock, MIN_BLOCKS) uniform_walk_staged_kernel(const UniformParams P) {
   constexpr int kPitch = 33;  // 8-byte slots per tile row: 32 lanes + 1 pad
   __shared__ unsigned long long tiles[kWarpsPerBlock][S][kPitch];
   const int lane = threadIdx.x & 31;
@@ -192,6 +267,7 @@ __global__ void __launch_bounds__(kBlock) uniform_walk_staged_kernel(const Unifo
   unsigned long long (*tile)[kPitch] = tiles[wib];
   const int64_t w0 = ((int64_t)blockIdx.x * kWarpsPerBlock + wib) * 32;
   if (w0 >= P.num_walks) return;  // whole warp leaves together
+  const L2Policy pol = make_policies(P.hints);
   const int64_t L = P.walk_length;
   const int nw = (int)min((int64_t)32, P.num_walks - w0);
   const bool live = lane < nw;
@@ -224,7 +300,7 @@ __global__ void __launch_bounds__(kBlock) uniform_walk_staged_kernel(const Unifo
       if (idx < total) {
         const int wi = (sc == S) ? idx / S : idx / sc;
         const int j = idx - wi * sc;
-        bits = __float_as_uint(__ldg(rand_span + (int64_t)wi * L + l0 + j));
+        bits = ld4(rand_span + (int64_t)wi * L + l0 + j, pol.stream);
       }
       pre[k] = bits;
     }
@@ -248,7 +324,7 @@ __global__ void __launch_bounds__(kBlock) uniform_walk_staged_kernel(const Unifo
     if (live) {
       for (int j = 0; j < sc; j++) {
         int64_t e = -1;
-        if (!parked) e = uniform_step<USE_DESC>(P, cur, __uint_as_float((uint32_t)tile[j][lane]));
+        if (!parked) e = uniform_step<USE_DESC>(P, pol, cur, parked, __uint_as_float((uint32_t)tile[j][lane]));
         tile[j][lane] = (unsigned long long)cur;
         if (HAS_EOUT) eout_span[(int64_t)lane * L + l0 + j] = e;
       }
@@ -260,10 +336,62 @@ __global__ void __launch_bounds__(kBlock) uniform_walk_staged_kernel(const Unifo
       if (idx < total) {
         const int wi = (sc == S) ? idx / S : idx / sc;
         const int j = idx - wi * sc;
-        out_span[(int64_t)wi * (L + 1) + 1 + l0 + j] = (int64_t)tile[j][wi];
+        st8(out_span + (int64_t)wi * (L + 1) + 1 + l0 + j, (int64_t)tile[j][wi], pol.stream);
       }
     }
     __syncwarp();
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// edge hash set: exact membership "is (x -> t) an edge" in about one 32-byte probe
+// ---------------------------------------------------------------------------------
+// Open addressing over buckets of 4 x 8-byte slots (one 32-byte sector, aligned);
+// key = (x << 32) | t, empty = all ones. A key lives in the first bucket of its probe
+// sequence that had room when it was inserted, so a lookup may stop at the first bucket
+// that still has an empty slot. Load factor <= 0.5 by construction of the table size.
+constexpr uint64_t kEdgeEmpty = ~0ull;
+constexpr int kEdgeSlotsPerBucket = 4;
+constexpr int kEdgeMaxProbe = 4096;  // buckets; far beyond anything a half-full table produces
+
+__host__ __device__ __forceinline__ uint64_t edge_key(uint64_t x, uint64_t t) { return (x << 32) | t; }
+
+__device__ __forceinline__ uint64_t edge_bucket(uint64_t key, uint64_t num_buckets) {
+  uint64_t z = key;
+  z ^= z >> 30; z *= 0xbf58476d1ce4e5b9ull;
+  z ^= z >> 27; z *= 0x94d049bb133111ebull;
+  z ^= z >> 31;
+  return __umul64hi(z, num_buckets);
+}
+
+__global__ void __launch_bounds__(kBlock) edgeset_build_kernel(const int64_t* __restrict__ rowptr,
+                                                               const int64_t* __restrict__ col,
+                                                               int64_t num_nodes, int64_t num_edges,
+                                                               unsigned long long* __restrict__ table,
+                                                               uint64_t num_buckets, uint32_t* flags) {
+  const int64_t stride = (int64_t)gridDim.x * kBlock;
+  for (int64_t e = (int64_t)blockIdx.x * kBlock + threadIdx.x; e < num_edges; e += stride) {
+    // source row of edge e: last v with rowptr[v] <= e
+    int64_t lo = 0, hi = num_nodes;
+    while (hi - lo > 1) {
+      const int64_t mid = lo + (hi - lo) / 2;
+      if (__ldg(rowptr + mid) <= e) lo = mid; else hi = mid;
+    }
+    const int64_t t = __ldg(col + e);
+    if ((uint64_t)t >= (uint64_t)num_nodes) { raise_flag(flags, WALK_B200_FLAG_BAD_NODE); continue; }
+    const uint64_t key = edge_key((uint64_t)lo, (uint64_t)t);
+    uint64_t b = edge_bucket(key, num_buckets);
+    bool placed = false;
+    for (int probe = 0; probe < kEdgeMaxProbe && !placed; probe++) {
+      unsigned long long* slot = table + b * kEdgeSlotsPerBucket;
+#pragma unroll
+      for (int k = 0; k < kEdgeSlotsPerBucket && !placed; k++) {
+        const unsigned long long old = atomicCAS(slot + k, kEdgeEmpty, key);
+        if (old == kEdgeEmpty || old == key) placed = true;
+      }
+      if (++b == num_buckets) b = 0;
+    }
+    if (!placed) raise_flag(flags, WALK_B200_FLAG_EDGESET_FULL);
   }
 }
 
@@ -274,10 +402,13 @@ struct Node2vecParams {
   const int64_t* rowptr;
   const int64_t* col;
   const uint64_t* desc;
+  const uint64_t* edgeset;
+  uint64_t edgeset_buckets;
   int64_t num_nodes, num_edges;
   const int64_t* start;
   int64_t num_walks;
   int32_t walk_length;
+  int32_t hints;
   uint32_t cut0, cut1, cut2;  // accept31 < cut_k  <=>  r < prob_k
   uint32_t key0, key1;
   uint64_t walk_index_base;
@@ -286,102 +417,186 @@ struct Node2vecParams {
   int64_t* e_out;
   uint32_t* flags;
   unsigned long long* counters;
+  unsigned long long* queue;  // launch-wide chunk counter, zero at launch
 };
 
-enum : int { ST_ROW = 0, ST_ATTEMPT = 1, ST_SEARCH = 2, ST_XROW = 3, ST_DONE = 4 };
+enum : int { ST_IDLE = 0, ST_START, ST_ROW, ST_ATTEMPT, ST_XROW, ST_SEARCH, ST_HASH };
+enum : int { MEMBER_SEARCH_PREV = 0, MEMBER_SEARCH_CAND = 1, MEMBER_HASH = 2 };
 
-// One thread per walk; one gather per loop trip.
+// Persistent warps; one walk per lane; one gather per loop trip whatever the lane is doing.
+//   ST_START    fetch the start node of a freshly assigned walk
 //   ST_ROW      fetch the bounds of the current node's row
 //   ST_ATTEMPT  draw a candidate edge (Philox) and gather col[e]
-//   ST_XROW     (general graphs) fetch the bounds of the candidate's row
+//   ST_XROW     (MEMBER_SEARCH_CAND) fetch the bounds of the candidate's row
 //   ST_SEARCH   one binary-search probe of the membership test
-// The membership test is only entered when it can change the outcome: the draw is
-// already known to be >= cut2 (not accepted outright), not accepted by the
-// return-to-previous rule, and < cut1. SYM searches the candidate x in the previous
-// node's row (bounds already in registers, row hot in cache); otherwise the previous
-// node t is searched in the candidate's row, as the reference's is_neighbor(x, t) does.
-template <typename idx_t, bool SYM, bool USE_DESC, bool HAS_EOUT, bool COUNT>
-__global__ void __launch_bounds__(kBlock) node2vec_walk_kernel(const Node2vecParams P) {
-  const int64_t i = (int64_t)blockIdx.x * kBlock + threadIdx.x;
-  const bool live = i < P.num_walks;
-  if (!COUNT && !live) return;
+//   ST_HASH     (MEMBER_HASH) one 32-byte bucket of the edge hash set
+// A lane whose walk ends takes the next unassigned walk of its warp's current chunk of
+// 32; a warp whose chunk is used up takes the next chunk from a launch-wide counter
+// (one atomicAdd per 32 walks). Walk cost varies by orders of magnitude (isolated start:
+// two trips; hub-heavy walk under strong rejection: thousands) and is tied to the bits
+// of the start id on generated graphs, so any static deal of walks to warps leaves part
+// of the machine idle for a good part of the launch. Draws are indexed by the walk's
+// global row, so which lane runs which walk does not change any result.
+// The membership test is only entered when it can change the outcome: the accept draw
+// is already known to be >= cut2 (not accepted outright), not accepted by the
+// return-to-previous rule, and < cut1. MEMBER_SEARCH_PREV (undirected graphs) searches
+// the candidate x in the previous node's sorted row; MEMBER_SEARCH_CAND searches the
+// previous node t in the candidate's row, as the reference's is_neighbor(x, t) does;
+// MEMBER_HASH asks the edge hash set for (x -> t).
+template <typename idx_t, int MEMBER, bool USE_DESC, bool HAS_EOUT, bool COUNT>
+__global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(const Node2vecParams P) {
+  constexpr unsigned kFull = 0xffffffffu;
+  const int lane = threadIdx.x & 31;
+  const L2Policy pol = make_policies(P.hints);
+  const int32_t L = P.walk_length;
+  const int64_t n = P.num_walks;
+  const int64_t* __restrict__ col = P.col;
 
-  uint32_t c_loads = 0, c_attempts = 0, c_member = 0, c_probes = 0;
+  // warp-uniform queue of walks: [q_next, q_end) of the current chunk of 32
+  const int64_t n_chunks = (n + 31) / 32;
+  int64_t q_next = 0, q_end = 0;  // empty: the first trip fetches a chunk
+  bool drained = false;           // the launch-wide counter has run past the last chunk
+
+  uint32_t c_loads = 0, c_attempts = 0, c_member = 0, c_probes = 0, c_formula = 0;
   uint32_t c_deg0 = 0, c_deg1 = 0, c_sampled = 0, c_first = 0;
 
-  if (live) {
-    const int32_t L = P.walk_length;
-    const uint64_t gw = P.walk_index_base + (uint64_t)i;
-    int64_t* out = P.n_out + i * ((int64_t)L + 1);
-    int64_t* eout = HAS_EOUT ? P.e_out + i * (int64_t)L : nullptr;
-    const int64_t* __restrict__ col = P.col;
+  int64_t i = 0;                  // walk (row of this launch) the lane is working on
+  idx_t t = 0, v = 0, x = 0;      // previous node, current node, candidate
+  idx_t v_rs = 0, v_re = 0;       // row [start, end) of v
+  idx_t t_rs = 0, t_re = 0;       // row [start, end) of t (MEMBER_SEARCH_PREV range)
+  uint32_t v_deg = 0;             // degree of v saturated at 2^31 (enough for "u % deg" with 31-bit u)
+  using uidx_t = typename std::conditional<sizeof(idx_t) == 4, uint32_t, uint64_t>::type;
+  uidx_t lo = 0, hi = 0;          // search window / hash bucket + probe count / parked accept draw
+  idx_t e = 0;                    // sampled edge index
+  int32_t l = 0;                  // step being produced
+  uint32_t a = 0;                 // attempt counter of this step
+  int state = ST_IDLE;
 
-    idx_t t, v, x = 0;              // previous node, current node, candidate
-    idx_t v_rs = 0, v_re = 0;       // row [start, end) of v
-    idx_t t_rs = 0, t_re = 0;       // row [start, end) of t (SYM search range)
-    uint32_t v_deg = 0;             // degree of v saturated at 2^31 (enough for "u % deg" with 31-bit u)
-    idx_t lo = 0, hi = 0;           // binary-search window
-    idx_t e = 0;                    // sampled edge index
-    int32_t l = 0;                  // step being produced
-    uint32_t a = 0;                 // attempt counter of this step
-    int state = ST_ROW;
-
-    const int64_t s0 = P.start[i];
-    out[0] = s0;
-    if ((uint64_t)s0 >= (uint64_t)P.num_nodes) {
-      raise_flag(P.flags, WALK_B200_FLAG_BAD_NODE);
-      for (int32_t k = 0; k < L; k++) { out[k + 1] = s0; if (HAS_EOUT) eout[k] = -1; }
-      state = ST_DONE;
+  while (true) {
+    // ---- hand walks to idle lanes (all lanes of the warp pass here together)
+    const unsigned idle = __ballot_sync(kFull, state == ST_IDLE);
+    if (idle) {
+      if (q_next >= q_end && !drained) {  // chunk used up: take the next one of the launch
+        unsigned long long chunk = 0;
+        if (lane == 0) chunk = atomicAdd(P.queue, 1ull);
+        chunk = __shfl_sync(kFull, chunk, 0);
+        if ((int64_t)chunk < n_chunks) {
+          q_next = (int64_t)chunk * 32;
+          q_end = min(q_next + 32, n);
+        } else {
+          drained = true;
+        }
+      }
+      if (q_next < q_end) {
+        const int avail = (int)(q_end - q_next);
+        const int rank = __popc(idle & ((1u << lane) - 1u));
+        if (state == ST_IDLE && rank < avail) {
+          i = q_next + rank;
+          state = ST_START;
+        }
+        q_next += min(__popc(idle), avail);
+      } else if (idle == kFull) {
+        break;  // nothing left to hand out and nobody is working
+      }
     }
-    if (L == 0) state = ST_DONE;
-    t = (idx_t)s0;
-    v = (idx_t)s0;
 
-    while (state != ST_DONE) {
+    if (state != ST_IDLE) {
+      int64_t* out = P.n_out + i * ((int64_t)L + 1);
+      int64_t* eout = HAS_EOUT ? P.e_out + i * (int64_t)L : nullptr;
+
       // ---- address of this trip's gather
-      const int64_t* addr;
-      if (state == ST_ROW) {
-        addr = USE_DESC ? (const int64_t*)(P.desc + (int64_t)v) : P.rowptr + (int64_t)v;
+      const void* addr;
+      uint64_t policy = pol.stream;
+      if (state == ST_START) {
+        addr = P.start + i;
+      } else if (state == ST_ROW) {
+        addr = USE_DESC ? (const void*)(P.desc + (int64_t)v) : (const void*)(P.rowptr + (int64_t)v);
+        policy = pol.keep;
       } else if (state == ST_ATTEMPT) {
         if (v_deg == 1) {
           e = v_rs;  // forced move: no draw (deg-1 shortcut of the reference; also exact at step 0)
         } else {
           uint32_t cand, acc;
-          node2vec_draw(P.key0, P.key1, gw, (uint32_t)l, a, cand, acc);
+          node2vec_draw(P.key0, P.key1, P.walk_index_base + (uint64_t)i, (uint32_t)l, a, cand, acc);
           e = v_rs + (idx_t)(cand % v_deg);
-          lo = (idx_t)acc;  // parked in `lo` until the candidate arrives
+          lo = acc;  // parked until the candidate arrives
         }
         addr = col + (int64_t)e;
       } else if (state == ST_XROW) {
-        addr = USE_DESC ? (const int64_t*)(P.desc + (int64_t)x) : P.rowptr + (int64_t)x;
-      } else {  // ST_SEARCH
+        addr = USE_DESC ? (const void*)(P.desc + (int64_t)x) : (const void*)(P.rowptr + (int64_t)x);
+        policy = pol.keep;
+      } else if (state == ST_SEARCH) {
         addr = col + (int64_t)(lo + (hi - lo) / 2);
+        policy = pol.normal;  // upper levels of a hub row's search tree are shared by many walks
+      } else {  // ST_HASH
+        addr = P.edgeset + (uint64_t)lo * kEdgeSlotsPerBucket;
       }
 
-      int64_t val = __ldg(addr);
-      int64_t val2 = 0;
-      if (!USE_DESC && (state == ST_ROW || state == ST_XROW)) val2 = __ldg(addr + 1);
-      if (COUNT) c_loads += (!USE_DESC && (state == ST_ROW || state == ST_XROW)) ? 2 : 1;
+      int64_t val = 0, val2 = 0;
+      ulonglong2 h0 = {0, 0}, h1 = {0, 0};
+      if (MEMBER == MEMBER_HASH && state == ST_HASH) {
+        h0 = ld16(addr, policy);
+        h1 = ld16((const char*)addr + 16, policy);
+        if (COUNT) c_loads += 4;
+      } else {
+        val = ld8(addr, policy);
+        const bool pair = !USE_DESC && (state == ST_ROW || state == ST_XROW);
+        if (pair) val2 = ld8((const char*)addr + 8, policy);
+        // the instrumented kernel's extra look at deg(x) is bookkeeping, not part of the walk
+        const bool bookkeeping = COUNT && state == ST_XROW && MEMBER != MEMBER_SEARCH_CAND;
+        if (COUNT && !bookkeeping) c_loads += pair ? 2 : 1;
+      }
 
       // ---- consume it
       bool accept = false, reject = false;
-      if (state == ST_ROW) {
+      if (state == ST_START) {
+        out[0] = val;
+        t = (idx_t)val;
+        v = (idx_t)val;
+        l = 0;
+        if ((uint64_t)val >= (uint64_t)P.num_nodes) {
+          raise_flag(P.flags, WALK_B200_FLAG_BAD_NODE);
+          for (int32_t k = 0; k < L; k++) { out[k + 1] = val; if (HAS_EOUT) eout[k] = -1; }
+          state = ST_IDLE;
+        } else {
+          state = L > 0 ? ST_ROW : ST_IDLE;
+        }
+      } else if (state == ST_ROW || state == ST_XROW) {
         int64_t rs, deg;
         if (USE_DESC) { rs = (int64_t)((uint64_t)val & kDescStartMask); deg = (int64_t)((uint64_t)val >> kDescStartBits); }
         else { rs = val; deg = val2 - val; }
         if (deg < 0 || rs < 0 || rs + deg > P.num_edges) { raise_flag(P.flags, WALK_B200_FLAG_BAD_ROWPTR); deg = 0; }
-        if (deg == 0) {
-          // stay in place for every remaining step
-          if (COUNT) c_deg0 += (uint32_t)(L - l);
-          for (int32_t k = l; k < L; k++) { out[k + 1] = (int64_t)v; if (HAS_EOUT) eout[k] = -1; }
-          state = ST_DONE;
-        } else {
-          v_rs = (idx_t)rs;
-          v_re = (idx_t)(rs + deg);
-          v_deg = deg > 0x7fffffffll ? 0x80000000u : (uint32_t)deg;
-          a = 0;
-          state = ST_ATTEMPT;
-          if (COUNT) { if (l == 0) c_first++; else if (deg == 1) c_deg1++; else c_sampled++; }
+        if (state == ST_ROW) {
+          if (deg == 0) {
+            // stay in place for every remaining step
+            if (COUNT) c_deg0 += (uint32_t)(L - l);
+            for (int32_t k = l; k < L; k++) { st8(out + k + 1, (int64_t)v, pol.stream); if (HAS_EOUT) eout[k] = -1; }
+            state = ST_IDLE;
+          } else {
+            v_rs = (idx_t)rs;
+            v_re = (idx_t)(rs + deg);
+            v_deg = deg > 0x7fffffffll ? 0x80000000u : (uint32_t)deg;
+            a = 0;
+            state = ST_ATTEMPT;
+            if (COUNT) { if (l == 0) c_first++; else if (deg == 1) c_deg1++; else c_sampled++; }
+          }
+        } else {  // ST_XROW: bounds of the candidate's row
+          if (COUNT && P.counters) {  // formula term of this membership test: ceil(log2(deg(x) + 1))
+            uint32_t bits = 0;
+            while ((1ull << bits) < (uint64_t)deg + 1) bits++;
+            c_formula += bits;
+          }
+          if (MEMBER == MEMBER_SEARCH_CAND) {
+            lo = (uidx_t)rs; hi = (uidx_t)(rs + deg);
+            if (lo < hi) state = ST_SEARCH; else reject = true;
+          } else if (MEMBER == MEMBER_SEARCH_PREV) {  // only reached in the instrumented kernel
+            lo = (uidx_t)t_rs; hi = (uidx_t)t_re;
+            if (lo < hi) state = ST_SEARCH; else reject = true;
+          } else {
+            lo = (uidx_t)edge_bucket(edge_key((uint64_t)x, (uint64_t)t), P.edgeset_buckets);
+            hi = 0;
+            state = ST_HASH;
+          }
         }
       } else if (state == ST_ATTEMPT) {
         if ((uint64_t)val >= (uint64_t)P.num_nodes) {
@@ -397,31 +612,36 @@ __global__ void __launch_bounds__(kBlock) node2vec_walk_kernel(const Node2vecPar
           if (acc < P.cut2) accept = true;
           else if (x == t && acc < P.cut0) accept = true;
           else if (acc < P.cut1) {
-            if (SYM) {
-              lo = t_rs; hi = t_re;
-              if (COUNT) c_member++;
+            if (COUNT) c_member++;
+            if (COUNT || MEMBER == MEMBER_SEARCH_CAND) {
+              state = ST_XROW;  // the instrumented kernel always looks at deg(x) for the byte formula
+            } else if (MEMBER == MEMBER_SEARCH_PREV) {
+              lo = (uidx_t)t_rs; hi = (uidx_t)t_re;
               if (lo < hi) state = ST_SEARCH; else reject = true;
             } else {
-              state = ST_XROW;
-              if (COUNT) c_member++;
+              lo = (uidx_t)edge_bucket(edge_key((uint64_t)x, (uint64_t)t), P.edgeset_buckets);
+              hi = 0;
+              state = ST_HASH;
             }
           } else reject = true;
         }
-      } else if (state == ST_XROW) {
-        int64_t rs, deg;
-        if (USE_DESC) { rs = (int64_t)((uint64_t)val & kDescStartMask); deg = (int64_t)((uint64_t)val >> kDescStartBits); }
-        else { rs = val; deg = val2 - val; }
-        if (deg < 0 || rs < 0 || rs + deg > P.num_edges) { raise_flag(P.flags, WALK_B200_FLAG_BAD_ROWPTR); deg = 0; }
-        lo = (idx_t)rs; hi = (idx_t)(rs + deg);
-        if (lo < hi) state = ST_SEARCH; else { reject = true; }
-      } else {  // ST_SEARCH
+      } else if (state == ST_SEARCH) {
         if (COUNT) c_probes++;
-        const idx_t mid = lo + (hi - lo) / 2;
-        const int64_t key = SYM ? (int64_t)x : (int64_t)t;
+        const uidx_t mid = lo + (hi - lo) / 2;
+        const int64_t key = MEMBER == MEMBER_SEARCH_PREV ? (int64_t)x : (int64_t)t;
         if (val == key) accept = true;       // member, and the draw is known to be < cut1
         else {
           if (val < key) lo = mid + 1; else hi = mid;
           if (!(lo < hi)) reject = true;     // not a member, and the draw is known to be >= cut2
+        }
+      } else {  // ST_HASH
+        if (COUNT) c_probes++;
+        const uint64_t key = edge_key((uint64_t)x, (uint64_t)t);
+        if (h0.x == key || h0.y == key || h1.x == key || h1.y == key) accept = true;
+        else if (h0.x == kEdgeEmpty || h0.y == kEdgeEmpty || h1.x == kEdgeEmpty || h1.y == kEdgeEmpty) reject = true;
+        else {
+          if (++lo == P.edgeset_buckets) lo = 0;
+          if (++hi >= (uidx_t)kEdgeMaxProbe) { raise_flag(P.flags, WALK_B200_FLAG_EDGESET_FULL); reject = true; }
         }
       }
 
@@ -430,16 +650,16 @@ __global__ void __launch_bounds__(kBlock) node2vec_walk_kernel(const Node2vecPar
         state = ST_ATTEMPT;
         if (a >= P.max_attempts) {
           raise_flag(P.flags, WALK_B200_FLAG_ATTEMPT_CAP);
-          x = v; e = v_rs; accept = true;  // give up on this step: stand still
+          x = v; accept = true;  // give up on this step: stand still
         }
       }
       if (accept) {
-        out[l + 1] = (int64_t)x;
-        if (HAS_EOUT) eout[l] = (x == v && a >= P.max_attempts) ? -1 : (int64_t)e;
+        st8(out + l + 1, (int64_t)x, pol.stream);
+        if (HAS_EOUT) eout[l] = (a >= P.max_attempts) ? -1 : (int64_t)e;
         t = v; t_rs = v_rs; t_re = v_re;
         v = x;
         l++;
-        state = (l == L) ? ST_DONE : ST_ROW;
+        state = (l == L) ? ST_IDLE : ST_ROW;
       }
     }
   }
@@ -450,12 +670,13 @@ __global__ void __launch_bounds__(kBlock) node2vec_walk_kernel(const Node2vecPar
     c[WALK_B200_CNT_MEMBERSHIP] = c_member; c[WALK_B200_CNT_PROBES] = c_probes;
     c[WALK_B200_CNT_STEPS_DEG0] = c_deg0; c[WALK_B200_CNT_STEPS_DEG1] = c_deg1;
     c[WALK_B200_CNT_STEPS_SAMPLED] = c_sampled; c[WALK_B200_CNT_STEPS_FIRST] = c_first;
+    c[WALK_B200_CNT_FORMULA_PROBES] = c_formula;
 #pragma unroll
     for (int k = 0; k < WALK_B200_COUNTER_COUNT; k++) {
       unsigned long long s = c[k];
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-      if ((threadIdx.x & 31) == 0 && s) atomicAdd(P.counters + k, s);
+      for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(kFull, s, o);
+      if (lane == 0 && s) atomicAdd(P.counters + k, s);
     }
   }
 }

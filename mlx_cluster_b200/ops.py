@@ -58,7 +58,7 @@ class WalkGraph:
     row start | degree << 36) so that a walk step fetches row bounds with one load."""
 
     def __init__(self, rowptr: torch.Tensor, col: torch.Tensor, *, symmetric: bool = False,
-                 use_rowdesc: bool = True, validate: bool = False, stream=None):
+                 use_rowdesc: bool = True, edgeset: bool = False, validate: bool = False, stream=None):
         if not rowptr.is_cuda:
             raise ValueError("WalkGraph needs CUDA tensors (use HostGraph for host arrays)")
         dev = rowptr.device
@@ -71,6 +71,8 @@ class WalkGraph:
         self.num_edges = col.numel()
         self.symmetric = bool(symmetric)
         self.rowdesc = None
+        self.edgeset = None
+        self.edgeset_buckets = 0
         self._version = (rowptr._version, col._version)
         with torch.cuda.device(dev):
             self.flags = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -88,10 +90,30 @@ class WalkGraph:
                 if not (f & _lib.FLAG_DESC_OVERFLOW):
                     self.rowdesc = desc
                 self.flags.zero_()
+            if edgeset and self.num_edges > 0:
+                self.build_edgeset(stream=stream)
+
+    def build_edgeset(self, stream=None):
+        """Build the edge hash set (16 bytes per edge) that turns node2vec's membership test
+        into about one 32-byte read. Any CSR: directed or not, rows sorted or not."""
+        if self.edgeset is not None:
+            return
+        with torch.cuda.device(self.device):
+            buckets = _lib.edgeset_buckets(self.num_edges)
+            table = torch.empty(buckets * 4, dtype=torch.int64, device=self.device)
+            csr = self.csr()
+            _lib.check(_lib.lib().walk_b200_edgeset_build(C.byref(csr), table.data_ptr(), buckets,
+                                                          self.flags.data_ptr(), _stream_handle(stream, self.device)))
+            f = int(self.flags.item())
+            self.flags.zero_()
+            if f:
+                raise ValueError(f"edge set build failed, status flags 0x{f:x}: {describe_flags(f)}")
+            self.edgeset, self.edgeset_buckets = table, buckets
 
     def csr(self) -> _lib.Csr:
         return _lib.Csr(self.rowptr.data_ptr(), _ptr(self.col), self.num_nodes, self.num_edges,
-                        _ptr(self.rowdesc), _lib.CSR_SYMMETRIC if self.symmetric else 0, 0)
+                        _ptr(self.rowdesc), _lib.CSR_SYMMETRIC if self.symmetric else 0, 0,
+                        _ptr(self.edgeset), self.edgeset_buckets)
 
     def validate(self, start: Optional[torch.Tensor] = None, *, check_sorted: bool = True, stream=None):
         """Raise ValueError when the CSR (and, if given, the start nodes) is malformed."""
@@ -109,7 +131,8 @@ class WalkGraph:
 def describe_flags(f: int) -> str:
     names = [(_lib.FLAG_BAD_NODE, "node id out of range"), (_lib.FLAG_BAD_EDGE, "edge index out of range (rand outside [0,1)?)"),
              (_lib.FLAG_ATTEMPT_CAP, "rejection attempt cap hit"), (_lib.FLAG_BAD_ROWPTR, "rowptr malformed"),
-             (_lib.FLAG_DESC_OVERFLOW, "row descriptor overflow"), (_lib.FLAG_UNSORTED_ROW, "row not strictly ascending")]
+             (_lib.FLAG_DESC_OVERFLOW, "row descriptor overflow"), (_lib.FLAG_UNSORTED_ROW, "row not strictly ascending"),
+             (_lib.FLAG_EDGESET_FULL, "edge hash set overflow")]
     return "; ".join(n for b, n in names if f & b) or "none"
 
 
@@ -131,12 +154,15 @@ def _key(rowptr, col, symmetric):
             str(rowptr.device), bool(symmetric))
 
 
-def prepare_graph(rowptr, col, *, symmetric: bool = False, validate: bool = False) -> "WalkGraph":
+def prepare_graph(rowptr, col, *, symmetric: bool = False, edgeset: bool = False,
+                  validate: bool = False) -> "WalkGraph":
     """Build (or fetch from a small cache) the device-side graph for these CSR tensors."""
     k = _key(rowptr, col, symmetric)
     g = _GRAPH_CACHE.get(k)
+    if g is not None and edgeset:
+        g.build_edgeset()
     if g is None:
-        g = WalkGraph(rowptr, col, symmetric=symmetric, validate=validate)
+        g = WalkGraph(rowptr, col, symmetric=symmetric, edgeset=edgeset, validate=validate)
         _GRAPH_CACHE[k] = g
         while len(_GRAPH_CACHE) > _CACHE_SIZE:
             _GRAPH_CACHE.popitem(last=False)
@@ -148,7 +174,8 @@ def prepare_graph(rowptr, col, *, symmetric: bool = False, validate: bool = Fals
 class HostGraph:
     """A CSR graph given as host arrays, uploaded once and kept resident on one device."""
 
-    def __init__(self, rowptr, col, *, symmetric: bool = False, validate: bool = False, device=None):
+    def __init__(self, rowptr, col, *, symmetric: bool = False, edgeset: bool = False, validate: bool = False,
+                 device=None):
         self.rowptr = _require(_as_cpu_tensor(rowptr), "rowptr", torch.int64)
         self.col = _require(_as_cpu_tensor(col), "col", torch.int64)
         self.num_nodes = self.rowptr.numel() - 1
@@ -158,7 +185,8 @@ class HostGraph:
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().walk_b200_graph_create(
                 self.rowptr.data_ptr(), _ptr(self.col), self.num_nodes, self.num_edges,
-                _lib.CSR_SYMMETRIC if symmetric else 0, int(validate), C.byref(h)))
+                (_lib.CSR_SYMMETRIC if symmetric else 0) | (_lib.CSR_WANT_EDGESET if edgeset else 0),
+                int(validate), C.byref(h)))
         self._h = h
 
     def device_bytes(self) -> int:
@@ -184,11 +212,11 @@ def _as_cpu_tensor(a):
     return torch.from_numpy(np.ascontiguousarray(a))
 
 
-def _host_graph(rowptr, col, symmetric, validate):
-    k = _key(rowptr, col, symmetric)
+def _host_graph(rowptr, col, symmetric, validate, edgeset=False):
+    k = _key(rowptr, col, symmetric) + (bool(edgeset),)
     g = _HOST_CACHE.get(k)
     if g is None:
-        g = HostGraph(rowptr, col, symmetric=symmetric, validate=validate)
+        g = HostGraph(rowptr, col, symmetric=symmetric, edgeset=edgeset, validate=validate)
         _HOST_CACHE[k] = g
         while len(_HOST_CACHE) > _CACHE_SIZE:
             _, old = _HOST_CACHE.popitem(last=False)
@@ -262,7 +290,8 @@ def random_walk(rowptr, col, start, rand, walk_length, *, stream=None, return_ed
 
 
 def rejection_sampling(rowptr, col, start, walk_length, p, q, *, stream=None, seed: int = 0,
-                       walk_index_base: int = 0, symmetric: bool = False, return_edges: bool = False,
+                       walk_index_base: int = 0, symmetric: bool = False, edgeset: bool = False,
+                       return_edges: bool = False,
                        return_counters: bool = False, check: bool = False,
                        out: Optional[torch.Tensor] = None, graph: Optional[WalkGraph] = None):
     """node2vec biased walk by rejection sampling (``rejection_sampling`` of the reference,
@@ -273,18 +302,20 @@ def rejection_sampling(rowptr, col, start, walk_length, p, q, *, stream=None, se
     attempt), so a call is reproducible, re-entrant and independent of how walks are
     sharded (``walk_index_base`` = global index of row 0 of this call). Every row of
     ``col`` must be sorted ascending. ``symmetric=True`` asserts an undirected graph and
-    lets the membership test search the previous node's row; results do not change.
+    lets the membership test search the previous node's row; ``edgeset=True`` builds (once
+    per graph, 16 bytes per edge) an exact edge hash set and tests membership with about
+    one 32-byte read instead, for any CSR; neither changes a result.
     Returns int64 ``[n, walk_length + 1]``.
     """
     L = _check_walk_length(walk_length)
     p, q = float(p), float(q)
     if not isinstance(start, torch.Tensor) or not start.is_cuda:
         return _rejection_sampling_host(rowptr, col, start, L, p, q, seed, walk_index_base, symmetric,
-                                        return_edges, out)
+                                        return_edges, out, edgeset)
     dev = start.device
     g = graph if graph is not None else prepare_graph(_require(rowptr, "rowptr", torch.int64, dev),
                                                       _require(col, "col", torch.int64, dev),
-                                                      symmetric=symmetric)
+                                                      symmetric=symmetric, edgeset=edgeset)
     _require(start, "start", torch.int64, g.device)
     n = start.numel()
     with torch.cuda.device(dev):
@@ -333,11 +364,11 @@ def _random_walk_host(rowptr, col, start, rand, L, return_edges, out):
     return (out, e_out) if return_edges else out
 
 
-def _rejection_sampling_host(rowptr, col, start, L, p, q, seed, base, symmetric, return_edges, out):
+def _rejection_sampling_host(rowptr, col, start, L, p, q, seed, base, symmetric, return_edges, out, edgeset=False):
     rowptr, col = _as_cpu_tensor(rowptr), _as_cpu_tensor(col)
     start = _require(_as_cpu_tensor(start), "start", torch.int64)
     n = start.numel()
-    g = _host_graph(rowptr, col, symmetric, False)
+    g = _host_graph(rowptr, col, symmetric, False, edgeset)
     out = _host_out(n, L, out)
     e_out = torch.empty((n, L), dtype=torch.int64, pin_memory=True) if return_edges else None
     with torch.cuda.device(g.device):

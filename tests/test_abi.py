@@ -34,7 +34,9 @@ def test_status_codes_and_flags_match_header():
     assert defs["WALK_B200_CSR_SYMMETRIC"] == _lib.CSR_SYMMETRIC
     n_counters = len(re.findall(r"^\s+WALK_B200_CNT_[A-Z0-9_]+", header, flags=re.M))
     assert n_counters == len(_lib.COUNTER_NAMES)
-    assert C.sizeof(_lib.Csr) == 48
+    assert C.sizeof(_lib.Csr) == 64
+    assert defs["WALK_B200_FLAG_EDGESET_FULL"] == _lib.FLAG_EDGESET_FULL
+    assert defs["WALK_B200_CSR_WANT_EDGESET"] == _lib.CSR_WANT_EDGESET
 
 
 def test_host_philox_matches_independent_implementation_and_oracle(walklib):
@@ -80,19 +82,25 @@ def test_shard_range_partitions(walklib):
 
 def test_argument_errors_before_any_launch(walklib):
     before = _lib.launch_count()
-    csr = _lib.Csr(None, None, 4, 0, None, 0, 0)
+    csr = _lib.Csr(None, None, 4, 0, None, 0, 0, None, 0)
     assert walklib.walk_b200_uniform_walk(None, None, None, 0, 0, None, None, None, None) == _lib.ERR_INVALID_ARG
     assert walklib.walk_b200_uniform_walk(C.byref(csr), None, None, 4, 3, None, None, None, None) == _lib.ERR_INVALID_ARG
     assert b"rowptr" in walklib.walk_b200_last_error()
-    csr = _lib.Csr(8, 8, -1, 0, None, 0, 0)
+    csr = _lib.Csr(8, 8, -1, 0, None, 0, 0, None, 0)
     assert walklib.walk_b200_node2vec_walk(C.byref(csr), None, 0, 1, 1.0, 1.0, 0, 0, None, None, None, None, None) \
         == _lib.ERR_INVALID_ARG
-    csr = _lib.Csr(8, 8, 4, 4, None, 0, 0)
+    csr = _lib.Csr(8, 8, 4, 4, None, 0, 0, None, 0)
     assert walklib.walk_b200_node2vec_walk(C.byref(csr), 8, 4, -1, 1.0, 1.0, 0, 0, 8, None, None, None, None) \
         == _lib.ERR_INVALID_ARG
     assert walklib.walk_b200_node2vec_walk(C.byref(csr), 8, 4, 2, 0.0, 1.0, 0, 0, 8, None, None, None, None) \
         == _lib.ERR_BAD_PQ
     assert walklib.walk_b200_set_tuning(b"no_such_knob", 1) == _lib.ERR_INVALID_ARG
+    # edge hash set: sizing is host arithmetic; a misaligned or undersized table is refused before any launch
+    assert _lib.edgeset_buckets(0) == 64 and _lib.edgeset_buckets(1000) == 500 and _lib.edgeset_buckets(1001) == 501
+    assert walklib.walk_b200_edgeset_build(C.byref(csr), 8, 64, None, None) == _lib.ERR_INVALID_ARG
+    big = _lib.Csr(8, 8, 4, 100000, None, 0, 0, None, 0)
+    assert walklib.walk_b200_edgeset_build(C.byref(big), 64, 64, None, None) == _lib.ERR_INVALID_ARG
+    assert b"too small" in walklib.walk_b200_last_error()
     assert _lib.launch_count() == before
     # empty batches succeed without touching the device
     assert walklib.walk_b200_uniform_walk(C.byref(csr), None, None, 0, 5, None, None, None, None) == 0

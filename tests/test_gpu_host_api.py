@@ -29,10 +29,10 @@ def test_host_arrays_uniform_and_biased(cuda, golden):
                          torch.from_numpy(g["rand2"]), 20, return_edges=True)
     np.testing.assert_array_equal(out.numpy(), g["uniform2_n"])
     np.testing.assert_array_equal(e.numpy(), g["uniform2_e"])
-    for sym in (False, True):
-        out = rejection_sampling(g["rowptr2"], g["col2"], g["start2"], 20, 0.5, 2.0, seed=4, symmetric=sym)
-        np.testing.assert_array_equal(out.numpy(), oracle.node2vec_walk(g["rowptr2"], g["col2"], g["start2"], 20,
-                                                                        0.5, 2.0, seed=4))
+    want = oracle.node2vec_walk(g["rowptr2"], g["col2"], g["start2"], 20, 0.5, 2.0, seed=4)
+    for kw in (dict(symmetric=False), dict(symmetric=True), dict(edgeset=True)):
+        out = rejection_sampling(g["rowptr2"], g["col2"], g["start2"], 20, 0.5, 2.0, seed=4, **kw)
+        np.testing.assert_array_equal(out.numpy(), want)
 
 
 def test_slab_pipeline_many_slabs(cuda):
@@ -80,6 +80,9 @@ def test_host_entry_reports_bad_input(cuda, golden):
     hg = HostGraph(g["rowptr1"], g["col1"], validate=True)
     assert hg.device_bytes() == (2709 + 10556 + 2708) * 8
     hg.close()
+    hg = HostGraph(g["rowptr1"], g["col1"], edgeset=True)
+    assert hg.device_bytes() == (2709 + 10556 + 2708) * 8 + _lib.edgeset_buckets(10556) * 32
+    hg.close()
 
 
 def test_l2_window_hint_does_not_change_results(cuda, golden):
@@ -95,3 +98,10 @@ def test_l2_window_hint_does_not_change_results(cuda, golden):
     np.testing.assert_array_equal(out.cpu().numpy(), g["uniform1_n"])
     _lib.check(_lib.lib().walk_b200_l2_window_clear(s.cuda_stream))
     assert granted.value in (0, graph.rowdesc.numel() * 8)
+
+
+def test_gather_probe_reports_a_plausible_rate(cuda):
+    rate = _lib.gather_probe(256 << 20, 8)
+    assert 1e9 < rate < 1e12
+    with pytest.raises(_lib.WalkError):
+        _lib.gather_probe(1024, 8)

@@ -21,13 +21,15 @@ PQS = [(1.0, 1.0), (0.5, 2.0), (4.0, 0.25), (0.25, 4.0), (1.0, 3.0)]
 def _reset_tuning():
     yield
     _lib.set_tuning("n2v_idx", 0)
+    _lib.set_tuning("l2_hints", 1)
 
 
 def run_gpu(dev, rowptr, col, start, L, p, q, *, seed=0, base=0, symmetric=False, rowdesc=True,
-            idx64=False, edges=True, counters=False):
+            idx64=False, edges=True, counters=False, edgeset=False):
     _lib.set_tuning("n2v_idx", 1 if idx64 else 0)
     g = WalkGraph(torch.from_numpy(rowptr).to(dev), torch.from_numpy(col).to(dev), symmetric=symmetric,
-                  use_rowdesc=rowdesc)
+                  use_rowdesc=rowdesc, edgeset=edgeset)
+    assert (g.edgeset is not None) == (edgeset and col.size > 0)
     res = rejection_sampling(None, None, torch.from_numpy(start).to(dev), L, p, q, graph=g, seed=seed,
                              walk_index_base=base, return_edges=edges, return_counters=counters, check=True)
     if not isinstance(res, tuple):
@@ -35,16 +37,25 @@ def run_gpu(dev, rowptr, col, start, L, p, q, *, seed=0, base=0, symmetric=False
     return tuple(r.cpu().numpy() if isinstance(r, torch.Tensor) else r for r in res)
 
 
+MEMBERSHIP = {"search_candidate_row": dict(symmetric=False), "search_previous_row": dict(symmetric=True),
+              "edge_hash_set": dict(edgeset=True)}
+
+
 @pytest.mark.parametrize("pq", PQS)
-@pytest.mark.parametrize("symmetric", [False, True])
-def test_small_workload_stream_exact(cuda, golden, pq, symmetric):
+@pytest.mark.parametrize("member", list(MEMBERSHIP))
+def test_small_workload_stream_exact(cuda, golden, pq, member):
     g = golden
     n_o, e_o, cnt = oracle.node2vec_walk(g["rowptr2"], g["col2"], g["start2"], 20, *pq, seed=42,
                                          return_edges=True, return_counters=True)
     for rowdesc in (True, False):
         for idx64 in (False, True):
             n, e, c = run_gpu(cuda, g["rowptr2"], g["col2"], g["start2"], 20, *pq, seed=42,
-                              symmetric=symmetric, rowdesc=rowdesc, idx64=idx64, counters=True)
+                              rowdesc=rowdesc, idx64=idx64, counters=True, **MEMBERSHIP[member])
+            # the uninstrumented kernel is a different instantiation: check it too
+            n_plain = run_gpu(cuda, g["rowptr2"], g["col2"], g["start2"], 20, *pq, seed=42,
+                              rowdesc=rowdesc, idx64=idx64, edges=False, **MEMBERSHIP[member])
+            np.testing.assert_array_equal(n_plain, n_o)
+            assert c["formula_probes"] == cnt["bsearch_probes"]
             assert n.shape == (2708, 21) and n.dtype == np.int64
             np.testing.assert_array_equal(n, n_o)
             np.testing.assert_array_equal(e, e_o)
@@ -90,8 +101,9 @@ def test_shard_invariance_and_seed(cuda, golden):
                                                           seed=9, walk_index_base=big_base))
 
 
+@pytest.mark.parametrize("edgeset", [False, True])
 @pytest.mark.parametrize("symmetric", [False, True])
-def test_ragged_shapes_and_directed_graphs(cuda, symmetric):
+def test_ragged_shapes_and_directed_graphs(cuda, symmetric, edgeset):
     rng = np.random.default_rng(21)
     for trial, (n_nodes, walks, L, avg) in enumerate([
             (40, 1, 1, 3.0), (40, 31, 2, 3.0), (40, 33, 7, 6.0), (200, 255, 9, 2.0), (200, 257, 16, 8.0),
@@ -101,11 +113,12 @@ def test_ragged_shapes_and_directed_graphs(cuda, symmetric):
         start = rng.integers(0, n_nodes, walks).astype(np.int64)
         for pq in [(0.25, 4.0), (2.0, 0.5), (1.0, 1.0)]:
             if L == 0:
-                n = run_gpu(cuda, rowptr, col, start, L, *pq, seed=trial, symmetric=symmetric, edges=False)
+                n = run_gpu(cuda, rowptr, col, start, L, *pq, seed=trial, symmetric=symmetric, edges=False,
+                            edgeset=edgeset)
                 np.testing.assert_array_equal(n[:, 0], start)
                 continue
             n_o, e_o = oracle.node2vec_walk(rowptr, col, start, L, *pq, seed=trial, return_edges=True)
-            n, e = run_gpu(cuda, rowptr, col, start, L, *pq, seed=trial, symmetric=symmetric)
+            n, e = run_gpu(cuda, rowptr, col, start, L, *pq, seed=trial, symmetric=symmetric, edgeset=edgeset)
             np.testing.assert_array_equal(n, n_o, err_msg=f"trial {trial} pq {pq}")
             np.testing.assert_array_equal(e, e_o, err_msg=f"trial {trial} pq {pq}")
 
@@ -117,8 +130,8 @@ def test_self_loops_and_degree_one_chains(cuda):
     start = np.array([0, 1, 2, 3] * 40, dtype=np.int64)
     for pq in PQS:
         n_o, e_o = oracle.node2vec_walk(rowptr, col, start, 30, *pq, seed=3, return_edges=True)
-        for sym in (False,):
-            n, e = run_gpu(cuda, rowptr, col, start, 30, *pq, seed=3, symmetric=sym)
+        for edgeset in (False, True):
+            n, e = run_gpu(cuda, rowptr, col, start, 30, *pq, seed=3, symmetric=False, edgeset=edgeset)
             np.testing.assert_array_equal(n, n_o)
             np.testing.assert_array_equal(e, e_o)
     m = 50
@@ -143,6 +156,10 @@ def test_medium_rmat_stream_exact(cuda):
                                         return_counters=True, check=True)
             np.testing.assert_array_equal(out.cpu().numpy(), n_o)
             assert c["attempts"] == cnt["attempts"] and c["membership"] == cnt["membership_needed"]
+            assert c["formula_probes"] == cnt["bsearch_probes"]
+        hashed = WalkGraph(rowptr, col, edgeset=True)
+        out = rejection_sampling(None, None, start, 40, *pq, graph=hashed, seed=77, check=True)
+        np.testing.assert_array_equal(out.cpu().numpy(), n_o)
 
 
 @pytest.mark.parametrize("pq", [(1.0, 1.0), (0.5, 2.0), (4.0, 0.25)])
@@ -191,8 +208,14 @@ def test_properties_at_scale(cuda):
     assert bool((rowptr.diff()[src[~moved]] == 0).all())
     general = rejection_sampling(rowptr, col, start, L, 0.25, 4.0, seed=3, symmetric=False, check=True)
     assert torch.equal(out, general)
+    hashed = WalkGraph(rowptr, col, edgeset=True)
+    assert torch.equal(out, rejection_sampling(None, None, start, L, 0.25, 4.0, graph=hashed, seed=3, check=True))
+    for hints in (0, 1):
+        _lib.set_tuning("l2_hints", hints)
+        assert torch.equal(out, rejection_sampling(None, None, start, L, 0.25, 4.0, graph=hashed, seed=3))
     _lib.set_tuning("n2v_idx", 1)
     assert torch.equal(out, rejection_sampling(rowptr, col, start, L, 0.25, 4.0, seed=3, symmetric=True))
+    assert torch.equal(out, rejection_sampling(None, None, start, L, 0.25, 4.0, graph=hashed, seed=3))
     # a sub-sample of rows against the CPU restatement
     rows = torch.arange(0, n_nodes, 997, device=cuda)
     n_o = oracle.node2vec_walk(rowptr.cpu().numpy(), col.cpu().numpy(), rows.cpu().numpy(), L, 0.25, 4.0, seed=3,

@@ -12,7 +12,8 @@ from tests.test_oracle import random_csr
 
 pytestmark = pytest.mark.gpu
 
-VARIANTS = {"direct": 1, "staged8": 2, "staged16": 3, "staged4": 4}
+VARIANTS = {"direct": 1, "staged8": 2, "staged16": 3, "staged4": 4, "staged16_40regs": 5, "staged8_32regs": 6,
+            "staged16_64regs": 7, "staged16_48regs": 8, "staged8_40regs": 9}
 
 
 @pytest.fixture(autouse=True)

@@ -33,7 +33,7 @@ def _walk_both_ways(dev, rowptr, col, n_walks, L, seed):
     flags = torch.zeros(1, dtype=torch.int32, device=dev)
     _lib.check(lib.walk_b200_rowdesc_pack(rowptr.data_ptr(), n_nodes, col.numel(), desc.data_ptr(),
                                           flags.data_ptr(), stream))
-    csr = _lib.Csr(rowptr.data_ptr(), col.data_ptr(), n_nodes, col.numel(), desc.data_ptr(), 0, 0)
+    csr = _lib.Csr(rowptr.data_ptr(), col.data_ptr(), n_nodes, col.numel(), desc.data_ptr(), 0, 0, None, 0)
     want_n = torch.empty((n_walks, L + 1), dtype=torch.int64, device=dev)
     want_e = torch.empty((n_walks, L), dtype=torch.int64, device=dev)
     _lib.check(lib.walk_b200_uniform_walk(C.byref(csr), start.data_ptr(), rand.data_ptr(), n_walks, L,
