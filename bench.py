@@ -37,6 +37,15 @@ WORKLOADS = {
     "node2vec_rmat22_p1q2": dict(kind="node2vec", scale=22, edge_factor=16, seed=3, L=40, p=1.0, q=2.0),
 }
 RMAT = dict(a=0.57, b=0.19, c=0.19, d=0.05)
+# DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures summarised under
+# profiles/: measured on the scale-20 case of each workload; the full-size figures are that measurement
+# scaled by the number of gathers issued (traffic is proportional to gathers; see the profile notes).
+NCU_TRAFFIC = {
+    "node2vec_rmat20": (43.9e9, "ncu, measured"),
+    "node2vec_rmat24": (43.9e9 * 16.05, "ncu on node2vec_rmat20 scaled by gathers issued (x16.05)"),
+    "uniform_rmat20": (4.56e9, "ncu, measured"),
+    "uniform_rmat22": (4.56e9 * 3.71, "ncu on uniform_rmat20 scaled by gathers issued (x3.71)"),
+}
 PHILOX_SEED = 20240607
 
 
@@ -360,7 +369,9 @@ def run_ours(args, wl):
     peak, peak_kind = measured_peak_gbs()
     achieved = allsum(alg_bytes / (kernel_ms * 1e-3) / 1e9) / world  # mean per-GPU GB/s
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "peak_source": f"of {peak_kind}", "traffic": None, "kernel": "node2vec_walk_kernel" if
+                "peak_source": f"of {peak_kind}",
+                "traffic": NCU_TRAFFIC.get(args.workload, (None, None))[0] if world == 1 else None,
+                "traffic_source": NCU_TRAFFIC.get(args.workload, (None, None))[1], "kernel": "node2vec_walk_kernel" if
                 wl["kind"] == "node2vec" else "uniform_walk_staged_kernel", "kernel_ms": kernel_ms,
                 "algorithmic_bytes_per_launch": alg_bytes, "gathered_bytes_per_launch": gathered_bytes,
                 "gathered_gbs": allsum(gathered_bytes / (kernel_ms * 1e-3) / 1e9) / world,
