@@ -195,7 +195,10 @@ int walk_b200_node2vec_walk_host(walk_b200_graph* g, const int64_t* h_start, int
 /* ---- L2 residency hint ----------------------------------------------------------
  * Marks [ptr, ptr+bytes) (typically rowdesc or rowptr: the array whose accesses are
  * skewed to hub nodes) as persisting in L2 for work launched on `stream` afterwards.
- * Per-context, per-stream state only; walk_b200_l2_window_clear undoes it.
+ * Per-context, per-stream state only; walk_b200_l2_window_clear undoes it, carve-out included.
+ * Measured on B200 with these kernels: the carve-out takes L2 away from the col gathers and made
+ * every workload slower (uniform scale 22: 5.9 -> 11.8 ms); the kernels' own per-load eviction
+ * policies do the job instead. Kept for hosts that want to experiment; off unless called.
  * granted_bytes (optional) receives the window actually set (0 if the device or
  * driver configuration offers none).
  */

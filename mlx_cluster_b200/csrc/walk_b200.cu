@@ -495,7 +495,8 @@ int walk_b200_l2_window_set(const void* ptr, size_t bytes, float hit_ratio, void
   CUDA_TRY(cudaDeviceGetAttribute(&max_window, cudaDevAttrMaxAccessPolicyWindowSize, dev));
   CUDA_TRY(cudaDeviceGetAttribute(&max_persist, cudaDevAttrMaxPersistingL2CacheSize, dev));
   if (max_window <= 0 || max_persist <= 0) return WALK_B200_OK;  // nothing on offer: not an error
-  if (cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, (size_t)max_persist) != cudaSuccess) {
+  const size_t carve = bytes < (size_t)max_persist ? bytes : (size_t)max_persist;
+  if (cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, carve) != cudaSuccess) {
     (void)cudaGetLastError();  // carve-out refused (e.g. a shared-context configuration): run without the hint
     return WALK_B200_OK;
   }
@@ -525,6 +526,8 @@ int walk_b200_l2_window_clear(void* stream) {
   attr.accessPolicyWindow.missProp = cudaAccessPropertyNormal;
   CUDA_TRY(cudaStreamSetAttribute((cudaStream_t)stream, cudaStreamAttributeAccessPolicyWindow, &attr));
   CUDA_TRY(cudaCtxResetPersistingL2Cache());
+  // give the carve-out back: while it is set aside, ordinary traffic has that much less L2
+  if (cudaDeviceSetLimit(cudaLimitPersistingL2CacheSize, 0) != cudaSuccess) (void)cudaGetLastError();
   return WALK_B200_OK;
 }
 
