@@ -241,7 +241,7 @@ def workload_config(wl, n_nodes, n_edges, gpus, membership=None):
     c = {"workload": args_workload_name(wl), "graph": f"R-MAT scale {wl['scale']} edge factor {wl['edge_factor']} "
          f"(a,b,c,d)=(0.57,0.19,0.19,0.05) seed {wl['seed']}, symmetrised, deduplicated, no self-loops, int64 CSR",
          "num_nodes": n_nodes, "num_directed_edges": n_edges, "starts": "every node once", "walk_length": wl["L"],
-         "sharding": f"start rows over {gpus} GPU(s), CSR replicated",
+         "sharding": f"start rows dealt cyclically over {gpus} GPU(s), CSR replicated",
          "l2": "no flush between steps: col (8 B x edges) is far larger than the 126 MB L2"}
     if wl["kind"] == "node2vec":
         c.update(p=wl["p"], q=wl["q"], draws="Philox4x32-10, key=seed, counter=(walk,step,attempt)",
@@ -289,7 +289,7 @@ def run_ours(args, wl):
     import torch.distributed as dist
     from mlx_cluster_b200 import _lib, random_walk, rejection_sampling
     from mlx_cluster_b200.ops import WalkGraph, HostGraph
-    from mlx_cluster_b200.sharding import shard_range
+    from mlx_cluster_b200.sharding import shard_rows
 
     rank, local_rank, world = env_rank()
     if not torch.cuda.is_available():
@@ -317,9 +317,11 @@ def run_ours(args, wl):
     _lib.lib()  # fail now if the CUDA library is missing
     rowptr, col, build_s = build_graph(wl, dev, world, rank)
     n_nodes, n_edges, L = rowptr.numel() - 1, col.numel(), wl["L"]
-    b, e = shard_range(n_nodes, world, rank)
-    rows = e - b
-    start = torch.arange(b, e, dtype=torch.int64, device=dev)
+    # cyclic shards (rank r walks start rows r, r + G, ...): block shards of an R-MAT graph differ by
+    # a quarter in work because node id and degree are correlated
+    row_slice, (b, stride) = shard_rows(n_nodes, world, rank, "cyclic")
+    start = torch.arange(n_nodes, dtype=torch.int64, device=dev)[row_slice].contiguous()
+    rows = start.numel()
     t_prep = time.perf_counter()
     graph = WalkGraph(rowptr, col, symmetric=True, edgeset=(wl["kind"] == "node2vec" and args.membership == "hash"))
     torch.cuda.synchronize(dev)
@@ -330,7 +332,8 @@ def run_ours(args, wl):
     if wl["kind"] == "node2vec":
         # untimed instrumented pass: counts the 8-byte gathers this batch needs
         _, cnt = rejection_sampling(None, None, start, L, wl["p"], wl["q"], graph=graph, seed=PHILOX_SEED,
-                                    walk_index_base=b, out=out, return_counters=True, check=True)
+                                    walk_index_base=b, walk_index_stride=stride, out=out, return_counters=True,
+                                    check=True)
         # algorithmic bytes of the reference's algorithm with a log-time membership test: per walk
         # 16; first step 32 (24 if isolated); stay-in-place step 24; degree-1 step 32; sampled step
         # 16 + 8 plus 8 per attempt plus, per membership test that can change the outcome,
@@ -344,7 +347,7 @@ def run_ours(args, wl):
 
         def step():
             rejection_sampling(None, None, start, L, wl["p"], wl["q"], graph=graph, seed=PHILOX_SEED,
-                               walk_index_base=b, out=out)
+                               walk_index_base=b, walk_index_stride=stride, out=out)
     else:
         gen = torch.Generator(device=dev).manual_seed(1234 + rank)
         rand = torch.rand((rows, L), generator=gen, device=dev)
@@ -410,7 +413,7 @@ def run_ours(args, wl):
         def host_step():
             if wl["kind"] == "node2vec":
                 _lib.check(_lib.lib().walk_b200_node2vec_walk_host(
-                    hg._h, h_start.data_ptr(), rows, L, wl["p"], wl["q"], PHILOX_SEED, b, h_out.data_ptr(), None))
+                    hg._h, h_start.data_ptr(), rows, L, wl["p"], wl["q"], PHILOX_SEED, b, stride, h_out.data_ptr(), None))
             else:
                 _lib.check(_lib.lib().walk_b200_uniform_walk_host(
                     hg._h, h_start.data_ptr(), h_rand.data_ptr(), rows, L, h_out.data_ptr(), None))

@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define WALK_B200_ABI_VERSION 2
+#define WALK_B200_ABI_VERSION 3
 
 /* ---- return codes ---- */
 #define WALK_B200_OK 0
@@ -109,7 +109,8 @@ int walk_b200_uniform_walk(const walk_b200_csr* g, const int64_t* start, const f
  * (random_walks/BiasedRandomWalk.cpp:30-102, is_neighbor :20-28); the reference has
  * no GPU version (eval_gpu throws, :150-155). Draws come from Philox4x32-10 with
  * key = seed and counter = (walk lo32, step, attempt, walk hi32), walk =
- * walk_index_base + row: word0>>1 picks the candidate (mod degree), word1>>1 is the
+ * walk_index_base + row * walk_index_stride (stride 0 is read as 1; a rank that holds every
+ * G-th start row passes base = its rank, stride = G): word0>>1 picks the candidate (mod degree), word1>>1 is the
  * accept draw r = w / 2147483647 compared against prob_0/1/2 of the reference
  * (:52-55). Same accept/reject decisions as the reference loop fed with that stream.
  * counters (device uint64[WALK_B200_COUNTER_COUNT]) selects the instrumented kernel
@@ -118,8 +119,8 @@ int walk_b200_uniform_walk(const walk_b200_csr* g, const int64_t* start, const f
  */
 int walk_b200_node2vec_walk(const walk_b200_csr* g, const int64_t* start, int64_t num_walks,
                             int32_t walk_length, double p, double q, uint64_t seed,
-                            uint64_t walk_index_base, int64_t* n_out, int64_t* e_out,
-                            uint32_t* status_flags, uint64_t* counters, void* stream);
+                            uint64_t walk_index_base, uint64_t walk_index_stride, int64_t* n_out,
+                            int64_t* e_out, uint32_t* status_flags, uint64_t* counters, void* stream);
 
 /*
  * Pack rowptr into one 8-byte descriptor per node: bits 0..35 = rowptr[v],
@@ -167,6 +168,10 @@ int walk_b200_node2vec_thresholds(double p, double q, double prob[3], uint32_t c
 /* Contiguous block partition of num_walks start rows over world_size ranks. */
 int walk_b200_shard_range(int64_t num_walks, int32_t world_size, int32_t rank,
                           int64_t* begin, int64_t* end);
+/* Cyclic partition: rank r holds rows r, r + world_size, ...; returns how many that is. Balances
+ * ranks on graphs whose node ids are correlated with degree (block shards of an R-MAT graph differ
+ * by 25 % in work). */
+int walk_b200_shard_count_cyclic(int64_t num_walks, int32_t world_size, int32_t rank, int64_t* count);
 
 /* ---- resident graph + host-buffer entry points ---------------------------------
  * For callers whose arrays live in host memory. The graph is uploaded once and stays
@@ -190,7 +195,8 @@ int walk_b200_uniform_walk_host(walk_b200_graph* g, const int64_t* h_start, cons
                                 int64_t* h_e_out);
 int walk_b200_node2vec_walk_host(walk_b200_graph* g, const int64_t* h_start, int64_t num_walks,
                                  int32_t walk_length, double p, double q, uint64_t seed,
-                                 uint64_t walk_index_base, int64_t* h_n_out, int64_t* h_e_out);
+                                 uint64_t walk_index_base, uint64_t walk_index_stride, int64_t* h_n_out,
+                                 int64_t* h_e_out);
 
 /* ---- L2 residency hint ----------------------------------------------------------
  * Marks [ptr, ptr+bytes) (typically rowdesc or rowptr: the array whose accesses are

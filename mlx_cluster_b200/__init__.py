@@ -4,8 +4,8 @@ computed by hand-written sm_100a CUDA kernels behind a C ABI (``include/walk_b20
 """
 from .ops import (HostGraph, WalkGraph, clear_caches, prepare_graph, random_walk, read_status,
                   rejection_sampling)
-from .sharding import shard_range, sharded_walk
+from .sharding import shard_range, shard_rows, sharded_walk
 
 __all__ = ["random_walk", "rejection_sampling", "prepare_graph", "WalkGraph", "HostGraph",
-           "read_status", "clear_caches", "shard_range", "sharded_walk"]
+           "read_status", "clear_caches", "shard_range", "shard_rows", "sharded_walk"]
 __version__ = "0.1.0"

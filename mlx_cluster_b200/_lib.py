@@ -24,7 +24,7 @@ EXPORTS = (
     "walk_b200_abi_version", "walk_b200_last_error", "walk_b200_launch_count",
     "walk_b200_uniform_walk", "walk_b200_node2vec_walk", "walk_b200_rowdesc_pack",
     "walk_b200_csr_validate", "walk_b200_edgeset_buckets", "walk_b200_edgeset_build", "walk_b200_philox4x32_10", "walk_b200_node2vec_draw",
-    "walk_b200_node2vec_thresholds", "walk_b200_shard_range",
+    "walk_b200_node2vec_thresholds", "walk_b200_shard_range", "walk_b200_shard_count_cyclic",
     "walk_b200_graph_create", "walk_b200_graph_destroy", "walk_b200_graph_csr",
     "walk_b200_graph_device_bytes", "walk_b200_uniform_walk_host", "walk_b200_node2vec_walk_host",
     "walk_b200_l2_window_set", "walk_b200_l2_window_clear",
@@ -63,7 +63,7 @@ def lib():
     L.walk_b200_last_error.restype = C.c_char_p
     L.walk_b200_launch_count.restype = u64
     L.walk_b200_uniform_walk.argtypes = [C.POINTER(Csr), vp, vp, i64, i32, vp, vp, vp, vp]
-    L.walk_b200_node2vec_walk.argtypes = [C.POINTER(Csr), vp, i64, i32, dbl, dbl, u64, u64, vp, vp, vp, vp, vp]
+    L.walk_b200_node2vec_walk.argtypes = [C.POINTER(Csr), vp, i64, i32, dbl, dbl, u64, u64, u64, vp, vp, vp, vp, vp]
     L.walk_b200_rowdesc_pack.argtypes = [vp, i64, i64, vp, vp, vp]
     L.walk_b200_csr_validate.argtypes = [C.POINTER(Csr), vp, i64, i32, vp, vp]
     L.walk_b200_edgeset_buckets.argtypes = [i64, C.POINTER(u64)]
@@ -74,12 +74,13 @@ def lib():
     L.walk_b200_node2vec_draw.restype = None
     L.walk_b200_node2vec_thresholds.argtypes = [dbl, dbl, C.POINTER(dbl * 3), C.POINTER(u32 * 3)]
     L.walk_b200_shard_range.argtypes = [i64, i32, i32, C.POINTER(i64), C.POINTER(i64)]
+    L.walk_b200_shard_count_cyclic.argtypes = [i64, i32, i32, C.POINTER(i64)]
     L.walk_b200_graph_create.argtypes = [vp, vp, i64, i64, u32, i32, C.POINTER(vp)]
     L.walk_b200_graph_destroy.argtypes = [vp]
     L.walk_b200_graph_csr.argtypes = [vp, C.POINTER(Csr)]
     L.walk_b200_graph_device_bytes.argtypes = [vp, C.POINTER(i64)]
     L.walk_b200_uniform_walk_host.argtypes = [vp, vp, vp, i64, i32, vp, vp]
-    L.walk_b200_node2vec_walk_host.argtypes = [vp, vp, i64, i32, dbl, dbl, u64, u64, vp, vp]
+    L.walk_b200_node2vec_walk_host.argtypes = [vp, vp, i64, i32, dbl, dbl, u64, u64, u64, vp, vp]
     L.walk_b200_l2_window_set.argtypes = [vp, C.c_size_t, C.c_float, vp, C.POINTER(C.c_size_t)]
     L.walk_b200_l2_window_clear.argtypes = [vp]
     L.walk_b200_uniform_walk_noalloc.argtypes = [vp, vp, i64, i64, vp, vp, i64, i32, vp, vp, vp, vp]
@@ -138,6 +139,12 @@ def gather_probe(array_bytes: int = 2 << 30, iters: int = 32) -> float:
     r = C.c_double(0.0)
     check(lib().walk_b200_gather_probe(array_bytes, iters, C.byref(r)))
     return float(r.value)
+
+
+def shard_count_cyclic(num_walks: int, world_size: int, rank: int) -> int:
+    c = C.c_int64(0)
+    check(lib().walk_b200_shard_count_cyclic(num_walks, world_size, rank, C.byref(c)))
+    return int(c.value)
 
 
 def edgeset_buckets(num_edges: int) -> int:

@@ -343,6 +343,14 @@ int walk_b200_shard_range(int64_t num_walks, int32_t world_size, int32_t rank, i
   return WALK_B200_OK;
 }
 
+int walk_b200_shard_count_cyclic(int64_t num_walks, int32_t world_size, int32_t rank, int64_t* count) {
+  if (num_walks < 0 || world_size < 1 || rank < 0 || rank >= world_size || !count)
+    return fail(WALK_B200_ERR_INVALID_ARG, "bad shard request (num_walks=%lld, world_size=%d, rank=%d)",
+                (long long)num_walks, world_size, rank);
+  *count = num_walks > rank ? (num_walks - rank + world_size - 1) / world_size : 0;
+  return WALK_B200_OK;
+}
+
 int walk_b200_uniform_walk(const walk_b200_csr* g, const int64_t* start, const float* rand,
                            int64_t num_walks, int32_t walk_length, int64_t* n_out, int64_t* e_out,
                            uint32_t* status_flags, void* stream) {
@@ -361,8 +369,8 @@ int walk_b200_uniform_walk(const walk_b200_csr* g, const int64_t* start, const f
 
 int walk_b200_node2vec_walk(const walk_b200_csr* g, const int64_t* start, int64_t num_walks,
                             int32_t walk_length, double p, double q, uint64_t seed,
-                            uint64_t walk_index_base, int64_t* n_out, int64_t* e_out,
-                            uint32_t* status_flags, uint64_t* counters, void* stream) {
+                            uint64_t walk_index_base, uint64_t walk_index_stride, int64_t* n_out,
+                            int64_t* e_out, uint32_t* status_flags, uint64_t* counters, void* stream) {
   if (int rc = check_csr(g)) return rc;
   if (int rc = check_walk_sizes(num_walks, walk_length, start, n_out)) return rc;
   double prob[3];
@@ -376,6 +384,7 @@ int walk_b200_node2vec_walk(const walk_b200_csr* g, const int64_t* start, int64_
   P.cut0 = cuts[0]; P.cut1 = cuts[1]; P.cut2 = cuts[2];
   P.key0 = (uint32_t)seed; P.key1 = (uint32_t)(seed >> 32);
   P.walk_index_base = walk_index_base;
+  P.walk_index_stride = walk_index_stride ? walk_index_stride : 1;
   P.max_attempts = WALK_B200_MAX_ATTEMPTS;
   P.n_out = n_out; P.e_out = walk_length > 0 ? e_out : nullptr;
   P.flags = status_flags; P.counters = (unsigned long long*)counters;
@@ -667,8 +676,9 @@ int flags_to_status(uint32_t f) {
 // per slab, slabs round-robin over kLanes streams so copies in both directions overlap
 // the kernels of neighbouring slabs.
 int run_host_walk(walk_b200_graph* g, bool biased, const int64_t* h_start, const float* h_rand,
-                  int64_t n, int32_t L, double p, double q, uint64_t seed, uint64_t base,
+                  int64_t n, int32_t L, double p, double q, uint64_t seed, uint64_t base, uint64_t stride,
                   int64_t* h_n_out, int64_t* h_e_out) {
+  if (stride == 0) stride = 1;
   if (!g) return fail(WALK_B200_ERR_INVALID_ARG, "graph handle is NULL");
   if (int rc = check_walk_sizes(n, L, h_start, h_n_out)) return rc;
   if (!biased && n > 0 && L > 0 && !h_rand) return fail(WALK_B200_ERR_INVALID_ARG, "rand is NULL");
@@ -707,8 +717,8 @@ int run_host_walk(walk_b200_graph* g, bool biased, const int64_t* h_start, const
     int64_t* d_e = (h_e_out && L > 0) ? g->d_eout[lane] : nullptr;
     int rc;
     if (biased) {
-      rc = walk_b200_node2vec_walk(&csr, g->d_start[lane], rows, L, p, q, seed, base + (uint64_t)r0,
-                                   g->d_out[lane], d_e, g->d_flags, nullptr, s);
+      rc = walk_b200_node2vec_walk(&csr, g->d_start[lane], rows, L, p, q, seed, base + (uint64_t)r0 * stride,
+                                   stride, g->d_out[lane], d_e, g->d_flags, nullptr, s);
     } else {
       if (L > 0)
         CUDA_TRY(cudaMemcpyAsync(g->d_rand[lane], h_rand + r0 * L, (size_t)rows * L * 4, cudaMemcpyHostToDevice, s));
@@ -829,13 +839,15 @@ int walk_b200_graph_device_bytes(const walk_b200_graph* g, int64_t* bytes) {
 
 int walk_b200_uniform_walk_host(walk_b200_graph* g, const int64_t* h_start, const float* h_rand,
                                 int64_t num_walks, int32_t walk_length, int64_t* h_n_out, int64_t* h_e_out) {
-  return run_host_walk(g, false, h_start, h_rand, num_walks, walk_length, 1.0, 1.0, 0, 0, h_n_out, h_e_out);
+  return run_host_walk(g, false, h_start, h_rand, num_walks, walk_length, 1.0, 1.0, 0, 0, 1, h_n_out, h_e_out);
 }
 
 int walk_b200_node2vec_walk_host(walk_b200_graph* g, const int64_t* h_start, int64_t num_walks,
                                  int32_t walk_length, double p, double q, uint64_t seed,
-                                 uint64_t walk_index_base, int64_t* h_n_out, int64_t* h_e_out) {
-  return run_host_walk(g, true, h_start, nullptr, num_walks, walk_length, p, q, seed, walk_index_base, h_n_out, h_e_out);
+                                 uint64_t walk_index_base, uint64_t walk_index_stride, int64_t* h_n_out,
+                                 int64_t* h_e_out) {
+  return run_host_walk(g, true, h_start, nullptr, num_walks, walk_length, p, q, seed, walk_index_base,
+                       walk_index_stride, h_n_out, h_e_out);
 }
 
 }  // extern "C"

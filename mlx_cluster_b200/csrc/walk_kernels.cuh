@@ -412,6 +412,7 @@ struct Node2vecParams {
   uint32_t cut0, cut1, cut2;  // accept31 < cut_k  <=>  r < prob_k
   uint32_t key0, key1;
   uint64_t walk_index_base;
+  uint64_t walk_index_stride;
   uint32_t max_attempts;
   int64_t* n_out;
   int64_t* e_out;
@@ -517,7 +518,7 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
           e = v_rs;  // forced move: no draw (deg-1 shortcut of the reference; also exact at step 0)
         } else {
           uint32_t cand, acc;
-          node2vec_draw(P.key0, P.key1, P.walk_index_base + (uint64_t)i, (uint32_t)l, a, cand, acc);
+          node2vec_draw(P.key0, P.key1, P.walk_index_base + (uint64_t)i * P.walk_index_stride, (uint32_t)l, a, cand, acc);
           e = v_rs + (idx_t)(cand % v_deg);
           lo = acc;  // parked until the candidate arrives
         }

@@ -290,7 +290,8 @@ def random_walk(rowptr, col, start, rand, walk_length, *, stream=None, return_ed
 
 
 def rejection_sampling(rowptr, col, start, walk_length, p, q, *, stream=None, seed: int = 0,
-                       walk_index_base: int = 0, symmetric: bool = False, edgeset: bool = False,
+                       walk_index_base: int = 0, walk_index_stride: int = 1, symmetric: bool = False,
+                       edgeset: bool = False,
                        return_edges: bool = False,
                        return_counters: bool = False, check: bool = False,
                        out: Optional[torch.Tensor] = None, graph: Optional[WalkGraph] = None):
@@ -300,7 +301,8 @@ def rejection_sampling(rowptr, col, start, walk_length, p, q, *, stream=None, se
     The reference draws from the C library's global ``rand()``; here the draws are a
     Philox4x32-10 stream keyed by ``seed`` and indexed by (global walk index, step,
     attempt), so a call is reproducible, re-entrant and independent of how walks are
-    sharded (``walk_index_base`` = global index of row 0 of this call). Every row of
+    sharded (row ``i`` of this call is global walk ``walk_index_base + i * walk_index_stride``).
+    Every row of
     ``col`` must be sorted ascending. ``symmetric=True`` asserts an undirected graph and
     lets the membership test search the previous node's row; ``edgeset=True`` builds (once
     per graph, 16 bytes per edge) an exact edge hash set and tests membership with about
@@ -311,7 +313,7 @@ def rejection_sampling(rowptr, col, start, walk_length, p, q, *, stream=None, se
     p, q = float(p), float(q)
     if not isinstance(start, torch.Tensor) or not start.is_cuda:
         return _rejection_sampling_host(rowptr, col, start, L, p, q, seed, walk_index_base, symmetric,
-                                        return_edges, out, edgeset)
+                                        return_edges, out, edgeset, walk_index_stride)
     dev = start.device
     g = graph if graph is not None else prepare_graph(_require(rowptr, "rowptr", torch.int64, dev),
                                                       _require(col, "col", torch.int64, dev),
@@ -330,7 +332,7 @@ def rejection_sampling(rowptr, col, start, walk_length, p, q, *, stream=None, se
         csr = g.csr()
         _lib.check(_lib.lib().walk_b200_node2vec_walk(
             C.byref(csr), _ptr(start), n, L, p, q, int(seed) & (2**64 - 1), int(walk_index_base),
-            _ptr(out), _ptr(e_out), g.flags.data_ptr(), _ptr(counters), _stream_handle(stream, dev)))
+            int(walk_index_stride), _ptr(out), _ptr(e_out), g.flags.data_ptr(), _ptr(counters), _stream_handle(stream, dev)))
     res = _finish(g, out, e_out, check, return_edges)
     if return_counters:
         cnt = dict(zip(_lib.COUNTER_NAMES, (int(x) for x in counters.tolist())))
@@ -364,7 +366,8 @@ def _random_walk_host(rowptr, col, start, rand, L, return_edges, out):
     return (out, e_out) if return_edges else out
 
 
-def _rejection_sampling_host(rowptr, col, start, L, p, q, seed, base, symmetric, return_edges, out, edgeset=False):
+def _rejection_sampling_host(rowptr, col, start, L, p, q, seed, base, symmetric, return_edges, out, edgeset=False,
+                             stride=1):
     rowptr, col = _as_cpu_tensor(rowptr), _as_cpu_tensor(col)
     start = _require(_as_cpu_tensor(start), "start", torch.int64)
     n = start.numel()
@@ -373,5 +376,5 @@ def _rejection_sampling_host(rowptr, col, start, L, p, q, seed, base, symmetric,
     e_out = torch.empty((n, L), dtype=torch.int64, pin_memory=True) if return_edges else None
     with torch.cuda.device(g.device):
         _lib.check(_lib.lib().walk_b200_node2vec_walk_host(g._h, _ptr(start), n, L, p, q, int(seed) & (2**64 - 1),
-                                                           int(base), _ptr(out), _ptr(e_out)))
+                                                           int(base), int(stride), _ptr(out), _ptr(e_out)))
     return (out, e_out) if return_edges else out

@@ -1,9 +1,13 @@
 """Sharding layer: start rows split across ranks, one process per GPU.
 
 Walks are independent, the CSR is replicated in every GPU's memory and read-only, so
-the walk itself needs no collective: rank ``r`` of ``G`` walks the contiguous block of
-start rows ``shard_range(n, G, r)``. node2vec draws are indexed by the *global* row, so
-the union of the shards is bit-identical to a single-GPU run whatever ``G`` is. The one
+the walk itself needs no collective. Two layouts: ``"block"`` -- rank ``r`` of ``G`` walks
+the contiguous rows ``shard_range(n, G, r)``; ``"cyclic"`` -- rank ``r`` walks rows
+``r, r + G, ...``. Cyclic is the default of the bench: on generated graphs node ids are
+correlated with degree (R-MAT: low ids are hubs, high ids are often isolated), and block
+shards then differ by a quarter in work. node2vec draws are indexed by the *global* row
+(``walk_index_base``/``walk_index_stride``), so the union of the shards is bit-identical
+to a single-GPU run whatever ``G`` and the layout are. The one
 optional exchange is the gather of the walk matrix to one rank, done with point-to-point
 sends posted as one batch (rows land at their global offset; the destination rank's own
 walk kernel writes straight into its slice of the gathered matrix).
@@ -29,6 +33,51 @@ def _world(group):
     if dist.is_available() and dist.is_initialized():
         return dist.get_world_size(group), dist.get_rank(group)
     return 1, 0
+
+
+def shard_rows(num_walks: int, world_size: int, rank: int, layout: str = "block"):
+    """The rows of rank ``rank`` as a ``slice`` (``start:stop:step``) and the
+    ``(walk_index_base, walk_index_stride)`` of its first row."""
+    if layout == "block":
+        b, e = shard_range(num_walks, world_size, rank)
+        return slice(b, e, 1), (b, 1)
+    if layout == "cyclic":
+        count = _lib.shard_count_cyclic(num_walks, world_size, rank)
+        return slice(rank, rank + count * world_size if count else rank, world_size), (rank, world_size)
+    raise ValueError(f"unknown layout {layout!r}")
+
+
+def gather_rows_cyclic(shard: torch.Tensor, num_rows: int, *, group=None, dst: int = 0,
+                       chunk_rows: int = 1 << 22):
+    """Collect cyclic shards on ``dst``: rank r's rows land at ``r::world``. Shards arrive in
+    a contiguous staging buffer of one shard and are interleaved by a strided copy."""
+    world, rank = _world(group)
+    if world == 1:
+        return shard
+    width = shard.shape[1]
+    if rank != dst:
+        ops = [dist.P2POp(dist.isend, shard[c0:min(shard.shape[0], c0 + chunk_rows)],
+                          dist.get_global_rank(group, dst) if group else dst, group)
+               for c0 in range(0, shard.shape[0], chunk_rows)]
+        for req in (dist.batch_isend_irecv(ops) if ops else []):
+            req.wait()
+        return None
+    full = torch.empty((num_rows, width), dtype=shard.dtype, device=shard.device)
+    full[rank::world].copy_(shard)
+    for r in range(world):
+        if r == dst:
+            continue
+        count = _lib.shard_count_cyclic(num_rows, world, r)
+        if count == 0:
+            continue
+        stage = torch.empty((count, width), dtype=shard.dtype, device=shard.device)
+        ops = [dist.P2POp(dist.irecv, stage[c0:min(count, c0 + chunk_rows)],
+                          dist.get_global_rank(group, r) if group else r, group)
+               for c0 in range(0, count, chunk_rows)]
+        for req in dist.batch_isend_irecv(ops):
+            req.wait()
+        full[r::world].copy_(stage)
+    return full
 
 
 def gather_rows(shard: torch.Tensor, num_rows: int, *, group=None, dst: int = 0,
@@ -76,29 +125,38 @@ def gather_rows(shard: torch.Tensor, num_rows: int, *, group=None, dst: int = 0,
 
 def sharded_walk(op: Callable[..., torch.Tensor], start: torch.Tensor, walk_length: int, *,
                  rand: Optional[torch.Tensor] = None, group=None, gather: bool = False, dst: int = 0,
-                 start_is_sharded: bool = False, num_walks: Optional[int] = None):
-    """Run ``op`` on this rank's block of start rows.
+                 start_is_sharded: bool = False, num_walks: Optional[int] = None, layout: str = "block"):
+    """Run ``op`` on this rank's share of the start rows.
 
-    ``op(start_shard, rand_shard, walk_index_base, out)`` must return the ``[rows,
-    walk_length + 1]`` matrix (written into ``out`` when ``out`` is not None); the product
-    callers pass a closure over :func:`random_walk` / :func:`rejection_sampling`.
-    ``start`` (and ``rand``) are either the full arrays, replicated on every rank
-    (default), or already this rank's block (``start_is_sharded=True`` with ``num_walks``
-    = global row count). Returns ``(shard, (begin, end))`` or, with ``gather=True``,
-    ``(full matrix on dst / None elsewhere, (begin, end))``.
+    ``op(start_shard, rand_shard, walk_index_base, out)`` (block layout) or
+    ``op(start_shard, rand_shard, (walk_index_base, walk_index_stride), out)`` (cyclic layout)
+    must return the ``[rows, walk_length + 1]`` matrix (written into ``out`` when ``out`` is not
+    None); the product callers pass a closure over :func:`random_walk` /
+    :func:`rejection_sampling`. ``start`` (and ``rand``) are either the full arrays, replicated on
+    every rank (default), or already this rank's share (``start_is_sharded=True`` with
+    ``num_walks`` = global row count). Returns ``(shard, rows)`` -- ``rows`` is ``(begin, end)``
+    for the block layout and the ``slice`` of global rows for the cyclic one -- or, with
+    ``gather=True``, the full matrix on ``dst`` (None elsewhere) in place of the shard.
     """
     world, rank = _world(group)
-    n = int(num_walks) if start_is_sharded else start.shape[0]
     if start_is_sharded and num_walks is None:
         raise ValueError("num_walks is required when start is already sharded")
-    b, e = shard_range(n, world, rank)
+    n = int(num_walks) if start_is_sharded else start.shape[0]
+    rows, (base, stride) = shard_rows(n, world, rank, layout)
+    count = len(range(*rows.indices(n))) if layout == "cyclic" else rows.stop - rows.start
     if start_is_sharded:
-        if start.shape[0] != e - b:
-            raise ValueError(f"rank {rank} expects {e - b} start rows, got {start.shape[0]}")
+        if start.shape[0] != count:
+            raise ValueError(f"rank {rank} expects {count} start rows, got {start.shape[0]}")
         s_shard, r_shard = start, rand
     else:
-        s_shard = start[b:e]
-        r_shard = None if rand is None else rand.reshape(n, -1)[b:e]
+        s_shard = start[rows].contiguous()
+        r_shard = None if rand is None else rand.reshape(n, -1)[rows].contiguous()
+    if layout == "cyclic":
+        shard = op(s_shard, r_shard, (base, stride), None)
+        if not gather:
+            return shard, rows
+        return gather_rows_cyclic(shard, n, group=group, dst=dst), rows
+    b, e = rows.start, rows.stop
     out_view = None
     full = None
     if gather and rank == dst and world > 1:

@@ -49,7 +49,7 @@ def _load_oracle():
         lib.oracle_accept_cut.restype = C.c_uint32
         lib.oracle_counter_count.restype = C.c_int
         lib.oracle_node2vec_walk.argtypes = [_I64P, _I64P, _I64P, C.c_int64, C.c_int, C.c_double,
-                                             C.c_double, C.c_int, C.c_uint64, C.c_uint64,
+                                             C.c_double, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64,
                                              _I64P, C.c_void_p, C.c_void_p]
         assert lib.oracle_counter_count() == len(COUNTER_NAMES)
         _oracle = lib
@@ -125,7 +125,8 @@ def uniform_walk(rowptr, col, start, rand, walk_length: int, return_edges: bool 
 
 
 def node2vec_walk(rowptr, col, start, walk_length: int, p: float, q: float, *, seed: int = 0,
-                  walk_index_base: int = 0, draw_mode: int = 1, return_edges: bool = False,
+                  walk_index_base: int = 0, walk_index_stride: int = 1, draw_mode: int = 1,
+                  return_edges: bool = False,
                   return_counters: bool = False):
     """draw_mode 1: Philox stream (key=seed, counter=(walk, step, attempt));
     draw_mode 0: libc rand() in the reference's call order (seed it with ``srand``)."""
@@ -138,7 +139,7 @@ def node2vec_walk(rowptr, col, start, walk_length: int, p: float, q: float, *, s
     if col.size == 0:
         col = np.zeros(1, dtype=np.int64)
     lib.oracle_node2vec_walk(rowptr, col, start if n else np.zeros(1, np.int64), n, walk_length,
-                             p, q, draw_mode, seed, walk_index_base,
+                             p, q, draw_mode, seed, walk_index_base, walk_index_stride,
                              n_out if n_out.size else np.zeros(1, np.int64), _opt(e_out), cnt.ctypes.data)
     res = [n_out]
     if return_edges:

@@ -145,13 +145,13 @@ int oracle_counter_count(void) { return CNT_COUNT; }
 
 /*
  * draw_mode 0: libc rand() in the reference's call order (caller seeds with srand()).
- * draw_mode 1: Philox stream above with global walk index walk_index_base + row.
+ * draw_mode 1: Philox stream above with global walk index walk_index_base + row * walk_index_stride.
  * counters: CNT_COUNT int64 slots, may be NULL.
  */
 void oracle_node2vec_walk(const int64_t* rowptr, const int64_t* col, const int64_t* start,
                           int64_t n, int walk_length, double p, double q,
                           int draw_mode, uint64_t seed, uint64_t walk_index_base,
-                          int64_t* n_out, int64_t* e_out /* may be NULL */,
+                          uint64_t walk_index_stride, int64_t* n_out, int64_t* e_out /* may be NULL */,
                           int64_t* counters /* may be NULL */) {
   const int64_t L = walk_length;
   double prob[3];
@@ -161,7 +161,7 @@ void oracle_node2vec_walk(const int64_t* rowptr, const int64_t* col, const int64
   memset(cnt, 0, sizeof(cnt));
 
   for (int64_t w = 0; w < n; w++) {
-    const uint64_t gw = walk_index_base + (uint64_t)w;
+    const uint64_t gw = walk_index_base + (uint64_t)w * (walk_index_stride ? walk_index_stride : 1);
     int64_t t = start[w], v, x = 0, e;
     n_out[w * (L + 1)] = t;
     if (L < 1) continue; /* the reference writes column 1 unconditionally; L >= 1 is its precondition */

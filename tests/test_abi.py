@@ -78,6 +78,10 @@ def test_shard_range_partitions(walklib):
             assert all(e - b <= per for b, e in spans)
     with pytest.raises(_lib.WalkError):
         _lib.shard_range(10, 2, 2)
+    for n in [0, 1, 7, 8, 9, 2708]:
+        for world in [1, 2, 3, 8]:
+            counts = [_lib.shard_count_cyclic(n, world, r) for r in range(world)]
+            assert counts == [len(range(r, n, world)) for r in range(world)]
 
 
 def test_argument_errors_before_any_launch(walklib):
@@ -87,12 +91,12 @@ def test_argument_errors_before_any_launch(walklib):
     assert walklib.walk_b200_uniform_walk(C.byref(csr), None, None, 4, 3, None, None, None, None) == _lib.ERR_INVALID_ARG
     assert b"rowptr" in walklib.walk_b200_last_error()
     csr = _lib.Csr(8, 8, -1, 0, None, 0, 0, None, 0)
-    assert walklib.walk_b200_node2vec_walk(C.byref(csr), None, 0, 1, 1.0, 1.0, 0, 0, None, None, None, None, None) \
+    assert walklib.walk_b200_node2vec_walk(C.byref(csr), None, 0, 1, 1.0, 1.0, 0, 0, 1, None, None, None, None, None) \
         == _lib.ERR_INVALID_ARG
     csr = _lib.Csr(8, 8, 4, 4, None, 0, 0, None, 0)
-    assert walklib.walk_b200_node2vec_walk(C.byref(csr), 8, 4, -1, 1.0, 1.0, 0, 0, 8, None, None, None, None) \
+    assert walklib.walk_b200_node2vec_walk(C.byref(csr), 8, 4, -1, 1.0, 1.0, 0, 0, 1, 8, None, None, None, None) \
         == _lib.ERR_INVALID_ARG
-    assert walklib.walk_b200_node2vec_walk(C.byref(csr), 8, 4, 2, 0.0, 1.0, 0, 0, 8, None, None, None, None) \
+    assert walklib.walk_b200_node2vec_walk(C.byref(csr), 8, 4, 2, 0.0, 1.0, 0, 0, 1, 8, None, None, None, None) \
         == _lib.ERR_BAD_PQ
     assert walklib.walk_b200_set_tuning(b"no_such_knob", 1) == _lib.ERR_INVALID_ARG
     # edge hash set: sizing is host arithmetic; a misaligned or undersized table is refused before any launch

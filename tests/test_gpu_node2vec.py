@@ -93,6 +93,12 @@ def test_shard_invariance_and_seed(cuda, golden):
         parts = [run_gpu(cuda, g["rowptr2"], g["col2"], g["start2"][b:e], 20, 0.5, 2.0, seed=9, base=b, edges=False)
                  for b, e in (_lib.shard_range(2708, world, r) for r in range(world))]
         np.testing.assert_array_equal(np.concatenate(parts), full)
+    for world in (2, 8):  # cyclic shards: rank r holds rows r::world, draws indexed base + i * stride
+        for r in range(world):
+            gq = WalkGraph(torch.from_numpy(g["rowptr2"]).to(cuda), torch.from_numpy(g["col2"]).to(cuda), edgeset=True)
+            part = rejection_sampling(None, None, torch.from_numpy(g["start2"][r::world].copy()).to(cuda), 20, 0.5, 2.0,
+                                      graph=gq, seed=9, walk_index_base=r, walk_index_stride=world, check=True)
+            np.testing.assert_array_equal(part.cpu().numpy(), full[r::world])
     other = run_gpu(cuda, g["rowptr2"], g["col2"], g["start2"], 20, 0.5, 2.0, seed=10, edges=False)
     assert (other != full).any()
     big_base = (1 << 33) + 5

@@ -48,6 +48,21 @@ def _worker(rank, world, port, n_rows, L, q):
             ok = ok and gathered is not None and np.array_equal(gathered.numpy(), full_expected)
         else:
             ok = ok and gathered is None
+        # cyclic layout: rank r walks rows r::world with draws indexed base + i * stride
+        def biased_cyclic(s, r, idx, out):
+            base, stride = idx
+            return torch.from_numpy(oracle.node2vec_walk(rowptr, col, s.numpy(), L, 0.5, 2.0, seed=3,
+                                                         walk_index_base=base, walk_index_stride=stride))
+
+        shard_c, rows_c = sharding.sharded_walk(biased_cyclic, start, L, layout="cyclic")
+        mine = len(range(rank, n_rows, world))
+        ok = ok and shard_c.shape[0] == mine and (mine == 0 or rows_c == slice(rank, rank + mine * world, world))
+        ok = ok and np.array_equal(shard_c.numpy(), full_expected[rank::world])
+        gathered_c, _ = sharding.sharded_walk(biased_cyclic, start, L, layout="cyclic", gather=True)
+        if rank == 0:
+            ok = ok and gathered_c is not None and np.array_equal(gathered_c.numpy(), full_expected)
+        else:
+            ok = ok and gathered_c is None
         # already-sharded inputs and a uniform op that consumes the rand block
         rng = np.random.default_rng(0)
         rand = torch.from_numpy(rng.random((n_rows, L), dtype=np.float32))
