@@ -237,7 +237,7 @@ def run_reference_arm(args, wl):
     return 0
 
 
-def workload_config(wl, n_nodes, n_edges, gpus, membership=None):
+def workload_config(wl, n_nodes, n_edges, gpus, membership=None, edge_records=None):
     c = {"workload": args_workload_name(wl), "graph": f"R-MAT scale {wl['scale']} edge factor {wl['edge_factor']} "
          f"(a,b,c,d)=(0.57,0.19,0.19,0.05) seed {wl['seed']}, symmetrised, deduplicated, no self-loops, int64 CSR",
          "num_nodes": n_nodes, "num_directed_edges": n_edges, "starts": "every node once", "walk_length": wl["L"],
@@ -247,7 +247,7 @@ def workload_config(wl, n_nodes, n_edges, gpus, membership=None):
         c.update(p=wl["p"], q=wl["q"], draws="Philox4x32-10, key=seed, counter=(walk,step,attempt)",
                  membership=membership)
     else:
-        c.update(rand="float32 uniform [0,1) [n, walk_length], caller-supplied")
+        c.update(rand="float32 uniform [0,1) [n, walk_length], caller-supplied", edge_records=edge_records)
     return c
 
 
@@ -323,7 +323,8 @@ def run_ours(args, wl):
     start = torch.arange(n_nodes, dtype=torch.int64, device=dev)[row_slice].contiguous()
     rows = start.numel()
     t_prep = time.perf_counter()
-    graph = WalkGraph(rowptr, col, symmetric=True, edgeset=(wl["kind"] == "node2vec" and args.membership == "hash"))
+    graph = WalkGraph(rowptr, col, symmetric=True, edgeset=(wl["kind"] == "node2vec" and args.membership == "hash"),
+                      fused=(wl["kind"] == "uniform" and not args.no_fused))
     torch.cuda.synchronize(dev)
     prep_s = time.perf_counter() - t_prep
     out = torch.empty((rows, L + 1), dtype=torch.int64, device=dev)
@@ -358,7 +359,8 @@ def run_ours(args, wl):
         stay = rows * L - moved
         # per step: row bounds 16 (8 via the packed descriptor, counted as the CSR's 16) + rand 4 + col 8 + out 8
         alg_bytes = rows * 16 + moved * 36 + stay * 24
-        gathered_bytes = rows * 16 + moved * 28 + stay * 12  # 8-byte descriptor instead of the 16-byte row pair
+        # 8-byte descriptor instead of the 16-byte row pair; fused records: one 16-byte gather per moving step
+        gathered_bytes = rows * 24 + moved * 28 if not args.no_fused else rows * 16 + moved * 28 + stay * 12
 
         def step():
             random_walk(None, None, start, rand, L, graph=graph, out=out)
@@ -389,7 +391,7 @@ def run_ours(args, wl):
             accesses = cnt["steps_first"] + cnt["steps_deg1"] + cnt["steps_sampled"] + rows \
                 + cnt["attempts"] + cnt["steps_first"] + cnt["steps_deg1"] + cnt["probes"]
         else:
-            accesses = 2 * moved + rows
+            accesses = (moved + 2 * rows) if not args.no_fused else (2 * moved + rows)
         roofline["random_access"] = {"ceiling_gathers_per_s": ceiling, "gathers_per_launch": int(accesses),
                                      "achieved_gathers_per_s": accesses / (kernel_ms * 1e-3),
                                      "frac": accesses / (kernel_ms * 1e-3) / ceiling,
@@ -405,7 +407,8 @@ def run_ours(args, wl):
         h_rand = rand.cpu().pin_memory() if rand is not None else None
         t_up = time.perf_counter()
         hg = HostGraph(h_rowptr, h_col, symmetric=True, device=dev,
-                       edgeset=(wl["kind"] == "node2vec" and args.membership == "hash"))
+                       edgeset=(wl["kind"] == "node2vec" and args.membership == "hash"),
+                       fused=(wl["kind"] == "uniform" and not args.no_fused))
         upload_s = time.perf_counter() - t_up
         del graph, out
         torch.cuda.empty_cache()
@@ -451,7 +454,9 @@ def run_ours(args, wl):
             "metric": "walk_steps_per_sec", "value": value, "unit": "steps/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
-            "config": workload_config(wl, n_nodes, n_edges, world, args.membership), "roofline": roofline, "cpu_baseline": cpu,
+            "config": workload_config(wl, n_nodes, n_edges, world, args.membership,
+                                      "col + row descriptors" if args.no_fused else "fused 16-byte records"),
+            "roofline": roofline, "cpu_baseline": cpu,
             "e2e": e2e, "gpu_launches": int(timed_launches), "clocks": clocks, "graph_build_s": build_s,
             "graph_prepare_s_once": prep_s,
         }
@@ -473,6 +478,7 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target CPU time of the cpu_baseline sample")
     ap.add_argument("--membership", default="hash", choices=["hash", "search"],
                     help="node2vec membership test: edge hash set (built once per graph) or binary search over col")
+    ap.add_argument("--no-fused", action="store_true", help="uniform walk: do not build fused edge records")
     ap.add_argument("--no-probe", action="store_true", help="skip the random-gather ceiling probe")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")

@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define WALK_B200_ABI_VERSION 3
+#define WALK_B200_ABI_VERSION 5
 
 /* ---- return codes ---- */
 #define WALK_B200_OK 0
@@ -56,7 +56,10 @@ extern "C" {
 #define WALK_B200_CSR_SYMMETRIC 0x1u /* caller asserts (u,v) in E <=> (v,u) in E: lets node2vec search the previous
                                         node's row instead of the candidate's; results are identical on such graphs */
 
-#define WALK_B200_CSR_WANT_EDGESET 0x2u /* walk_b200_graph_create only: also build the edge hash set */
+#define WALK_B200_CSR_WANT_EDGESET 0x2u /* walk_b200_graph_create only: also build the edge hash set and, when rows are
+                                           strictly ascending, the reverse positions */
+
+#define WALK_B200_CSR_WANT_FUSED 0x4u /* walk_b200_graph_create only: also build the fused edge records */
 
 typedef struct walk_b200_csr {
   const int64_t* rowptr;   /* device, [num_nodes + 1] */
@@ -69,6 +72,10 @@ typedef struct walk_b200_csr {
   const uint64_t* edgeset; /* device, [4 * edgeset_buckets], from walk_b200_edgeset_build, or NULL: node2vec then
                               runs its membership test as a binary search over col */
   uint64_t edgeset_buckets;
+  const uint32_t* revpos;  /* device, [num_edges], from walk_b200_revpos_build, or NULL; only used together with
+                              edgeset and rowdesc */
+  const void* fused;       /* device, [num_edges] 16-byte records from walk_b200_fused_build, or NULL; the uniform
+                              walk then makes one gather per step; needs rowdesc */
 } walk_b200_csr;
 
 /* node2vec instrumentation slots (device uint64[WALK_B200_COUNTER_COUNT], caller zeroes them) */
@@ -144,6 +151,27 @@ int walk_b200_rowdesc_pack(const int64_t* rowptr, int64_t num_nodes, int64_t num
 int walk_b200_edgeset_buckets(int64_t num_edges, uint64_t* buckets);
 int walk_b200_edgeset_build(const walk_b200_csr* g, uint64_t* table, uint64_t buckets,
                             uint32_t* status_flags, void* stream);
+
+/*
+ * Fused edge records for the uniform walk: fused[e] = (col[e], row descriptor of col[e]), 16 bytes per
+ * edge (caller scratch of 16 * num_edges bytes, 16-byte aligned; g->rowdesc must be set). The step
+ * "col[rowptr[v] + idx] then rowptr pair of the new node" (random_walks/RandomWalk.cpp:45-54) becomes
+ * one 16-byte gather, i.e. one DRAM access instead of two on graphs whose row bounds do not stay in L2.
+ * Results are identical with and without it.
+ */
+int walk_b200_fused_build(const walk_b200_csr* g, void* fused, uint32_t* status_flags, void* stream);
+
+/*
+ * Reverse positions: revpos[e] for the edge e = (u -> v) is the index in col of (v -> u), or
+ * 0xffffffff if the graph has no such edge. With it (and the edge hash set and row descriptors) a
+ * node2vec step knows without a gather whether a drawn edge leads back to the previous node --
+ * the "x == t" test of random_walks/BiasedRandomWalk.cpp:86 -- and skips the col gather of every
+ * attempt that only the return rule could accept (three in four at p=0.25, q=4). revpos is caller
+ * scratch of 4 * num_edges bytes. Needs every row strictly ascending (else
+ * WALK_B200_FLAG_UNSORTED_ROW is raised and the array must not be used) and num_edges < 2^32 - 2.
+ * Results are identical with and without it.
+ */
+int walk_b200_revpos_build(const walk_b200_csr* g, uint32_t* revpos, uint32_t* status_flags, void* stream);
 
 /*
  * Full check the reference never makes (it reinterprets whatever it is given,

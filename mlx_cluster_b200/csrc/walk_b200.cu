@@ -53,8 +53,10 @@ int check_launch(const char* what) {
 struct Tuning {
   std::atomic<int32_t> uniform_variant{0};  // 0 auto, 1 direct, 2 staged S=8, 3 staged S=16, 4 staged S=4,
                                             // 5 staged S=16 capped at 40 registers, 6 staged S=8 capped at 32
+  std::atomic<int32_t> uniform_fused{1};    // use fused edge records when the graph has them
   std::atomic<int32_t> n2v_idx{0};          // 0 auto (32-bit indices when they fit), 1 force 64-bit
   std::atomic<int32_t> n2v_member{0};       // 0 auto (hash set when the graph has one), 1 ignore the hash set
+  std::atomic<int32_t> n2v_rev{1};          // 1 auto (reverse positions when they pay), 0 never, 2 whenever available
   std::atomic<int32_t> n2v_blocks_per_sm{0};  // 0 = what the occupancy calculator allows
   std::atomic<int32_t> l2_hints{3};         // bit 0: evict-last row bounds, bit 1: evict-first streams
   std::atomic<int32_t> l2_fetch_granularity{0};  // set only through walk_b200_set_tuning (applies the CUDA limit)
@@ -65,8 +67,10 @@ struct Tuning {
 std::atomic<int32_t>* tuning_slot(const char* key) {
   if (!key) return nullptr;
   if (!strcmp(key, "uniform_variant")) return &g_tuning.uniform_variant;
+  if (!strcmp(key, "uniform_fused")) return &g_tuning.uniform_fused;
   if (!strcmp(key, "n2v_idx")) return &g_tuning.n2v_idx;
   if (!strcmp(key, "n2v_member")) return &g_tuning.n2v_member;
+  if (!strcmp(key, "n2v_rev")) return &g_tuning.n2v_rev;
   if (!strcmp(key, "n2v_blocks_per_sm")) return &g_tuning.n2v_blocks_per_sm;
   if (!strcmp(key, "l2_hints")) return &g_tuning.l2_hints;
   if (!strcmp(key, "l2_fetch_granularity")) return &g_tuning.l2_fetch_granularity;
@@ -134,6 +138,14 @@ int launch_uniform_t(const UniformParams& P, cudaStream_t s) {
   int variant = g_tuning.uniform_variant.load();
   if (variant == 0) variant = P.walk_length >= 4 ? 7 : 1;
   const unsigned grid = (unsigned)blocks_for(P.num_walks);
+  if (USE_DESC && P.fused && variant != 1 && g_tuning.uniform_fused.load() != 0) {
+    if (variant == 2) {
+      uniform_walk_staged_kernel<8, 1, true, HAS_EOUT, true><<<grid, kBlock, 0, s>>>(P);
+      return check_launch("uniform_walk_staged_kernel<8,fused>");
+    }
+    uniform_walk_staged_kernel<16, 4, true, HAS_EOUT, true><<<grid, kBlock, 0, s>>>(P);
+    return check_launch("uniform_walk_staged_kernel<16,4,fused>");
+  }
   switch (variant) {
     case 1:
       uniform_walk_direct_kernel<USE_DESC, HAS_EOUT><<<grid, kBlock, 0, s>>>(P);
@@ -256,10 +268,32 @@ int launch_n2v_i(const Node2vecParams& P, int member, cudaStream_t s) {
   }
 }
 
+// The reverse-position shortcut costs one more 4-byte gather per step and saves the col gather of
+// every attempt whose accept draw lies above both cut1 and cut2. Measured on R-MAT scale 24:
+// (p,q)=(0.25,4) 266 -> 199 ms, (0.5,2) 92 -> 88 ms, but (1,2) 64 -> 80 ms and (1,1) 27 -> 45 ms,
+// where no attempt can be skipped. It is used when at least half of the attempts are skippable.
+bool rev_pays(const Node2vecParams& P) {
+  const int mode = g_tuning.n2v_rev.load();
+  if (mode == 0) return false;
+  if (mode == 2) return true;
+  const uint32_t top = P.cut1 > P.cut2 ? P.cut1 : P.cut2;
+  return top <= (1u << 30);  // max(prob_1, prob_2) <= 0.5
+}
+
 int launch_n2v(const Node2vecParams& P, bool sym, cudaStream_t s) {
   int member = sym ? MEMBER_SEARCH_PREV : MEMBER_SEARCH_CAND;
   if (P.edgeset && P.edgeset_buckets > 0 && g_tuning.n2v_member.load() != 1) member = MEMBER_HASH;
   const bool fits32 = P.num_nodes <= 0x7fffffffll && P.num_edges <= 0xffffffffll;
+  if (member == MEMBER_HASH && P.revpos && P.desc && fits32 && P.num_edges < 0xfffffffell &&
+      g_tuning.n2v_idx.load() != 1 && rev_pays(P)) {
+    const bool e = P.e_out != nullptr, c = P.counters != nullptr;
+    if (c) {
+      if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, true, true, true>, P, s);
+      return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, false, true, true>, P, s);
+    }
+    if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, true, false, true>, P, s);
+    return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, false, false, true>, P, s);
+  }
   if (fits32 && g_tuning.n2v_idx.load() != 1) return launch_n2v_i<uint32_t>(P, member, s);
   return launch_n2v_i<int64_t>(P, member, s);
 }
@@ -364,6 +398,11 @@ int walk_b200_uniform_walk(const walk_b200_csr* g, const int64_t* start, const f
   P.start = start; P.rand = rand; P.num_walks = num_walks; P.walk_length = walk_length;
   P.n_out = n_out; P.e_out = walk_length > 0 ? e_out : nullptr; P.flags = status_flags;
   P.hints = g_tuning.l2_hints.load();
+  if (g->fused && g->rowdesc) {
+    if ((reinterpret_cast<uintptr_t>(g->fused) & 15) != 0)
+      return fail(WALK_B200_ERR_INVALID_ARG, "fused edge records must be 16-byte aligned");
+    P.fused = static_cast<const ulonglong2*>(g->fused);
+  }
   return launch_uniform(P, (cudaStream_t)stream);
 }
 
@@ -395,6 +434,7 @@ int walk_b200_node2vec_walk(const walk_b200_csr* g, const int64_t* start, int64_
     if ((reinterpret_cast<uintptr_t>(g->edgeset) & 31) != 0)
       return fail(WALK_B200_ERR_INVALID_ARG, "edgeset must be 32-byte aligned");
     P.edgeset = g->edgeset; P.edgeset_buckets = g->edgeset_buckets;
+    P.revpos = g->revpos;
   }
   return launch_n2v(P, (g->flags & WALK_B200_CSR_SYMMETRIC) != 0, (cudaStream_t)stream);
 }
@@ -433,6 +473,29 @@ int walk_b200_edgeset_build(const walk_b200_csr* g, uint64_t* table, uint64_t bu
   edgeset_build_kernel<<<grid_for_streaming(g->num_edges), kBlock, 0, (cudaStream_t)stream>>>(
       g->rowptr, g->col, g->num_nodes, g->num_edges, (unsigned long long*)table, buckets, status_flags);
   return check_launch("edgeset_build_kernel");
+}
+
+int walk_b200_fused_build(const walk_b200_csr* g, void* fused, uint32_t* status_flags, void* stream) {
+  if (int rc = check_csr(g)) return rc;
+  if (!g->rowdesc) return fail(WALK_B200_ERR_INVALID_ARG, "fused edge records need the row descriptors (rowdesc is NULL)");
+  if (g->num_edges > 0 && !fused) return fail(WALK_B200_ERR_INVALID_ARG, "fused is NULL");
+  if ((reinterpret_cast<uintptr_t>(fused) & 15) != 0)
+    return fail(WALK_B200_ERR_INVALID_ARG, "fused edge records must be 16-byte aligned");
+  if (g->num_edges == 0) return WALK_B200_OK;
+  fused_build_kernel<<<grid_for_streaming(g->num_edges), kBlock, 0, (cudaStream_t)stream>>>(
+      g->col, g->rowdesc, g->num_nodes, g->num_edges, static_cast<ulonglong2*>(fused), status_flags);
+  return check_launch("fused_build_kernel");
+}
+
+int walk_b200_revpos_build(const walk_b200_csr* g, uint32_t* revpos, uint32_t* status_flags, void* stream) {
+  if (int rc = check_csr(g)) return rc;
+  if (g->num_edges > 0 && !revpos) return fail(WALK_B200_ERR_INVALID_ARG, "revpos is NULL");
+  if (g->num_edges >= 0xfffffffell)
+    return fail(WALK_B200_ERR_UNSUPPORTED, "reverse positions are 32-bit: num_edges must be below 2^32 - 2");
+  if (g->num_edges == 0) return WALK_B200_OK;
+  revpos_build_kernel<<<grid_for_streaming(g->num_edges), kBlock, 0, (cudaStream_t)stream>>>(
+      g->rowptr, g->col, g->num_nodes, g->num_edges, revpos, status_flags);
+  return check_launch("revpos_build_kernel");
 }
 
 int walk_b200_csr_validate(const walk_b200_csr* g, const int64_t* start, int64_t num_walks,
@@ -622,6 +685,8 @@ struct walk_b200_graph {
   uint64_t* d_desc = nullptr;
   uint64_t* d_edgeset = nullptr;
   uint64_t edgeset_buckets = 0;
+  uint32_t* d_revpos = nullptr;
+  void* d_fused = nullptr;
   uint32_t* d_flags = nullptr;
   static constexpr int kLanes = 3;  // slabs in flight: copy-in, kernel, copy-out
   cudaStream_t streams[kLanes] = {};
@@ -708,6 +773,8 @@ int run_host_walk(walk_b200_graph* g, bool biased, const int64_t* h_start, const
   csr.rowptr = g->d_rowptr; csr.col = g->d_col; csr.num_nodes = g->num_nodes; csr.num_edges = g->num_edges;
   csr.rowdesc = g->d_desc; csr.flags = g->csr_flags;
   csr.edgeset = g->d_edgeset; csr.edgeset_buckets = g->edgeset_buckets;
+  csr.revpos = g->d_revpos;
+  csr.fused = g->d_fused;
 
   int lane = 0;
   for (int64_t r0 = 0; r0 < n; r0 += slab_rows, lane = (lane + 1) % walk_b200_graph::kLanes) {
@@ -793,6 +860,28 @@ int walk_b200_graph_create(const int64_t* h_rowptr, const int64_t* h_col, int64_
     G_TRY(cudaMemcpyAsync(&f, g->d_flags, 4, cudaMemcpyDeviceToHost, s));
     G_TRY(cudaStreamSynchronize(s));
     if (f) { flags_to_status(f); return bail(fail(WALK_B200_ERR_CSR_INVALID, "edge set build failed: %s", std::string(g_last_error).c_str())); }
+    // reverse positions ride on the edge set; rows that are not strictly ascending simply go without
+    if (num_edges < 0xfffffffell) {
+      G_TRY(cudaMalloc((void**)&g->d_revpos, (size_t)num_edges * sizeof(uint32_t)));
+      if (int rc = walk_b200_revpos_build(&csr, g->d_revpos, g->d_flags, s)) return bail(rc);
+      G_TRY(cudaMemcpyAsync(&f, g->d_flags, 4, cudaMemcpyDeviceToHost, s));
+      G_TRY(cudaStreamSynchronize(s));
+      if (f) {
+        cudaFree(g->d_revpos);
+        g->d_revpos = nullptr;
+        G_TRY(cudaMemsetAsync(g->d_flags, 0, 4, s));
+      }
+    }
+  }
+  if ((csr_flags & WALK_B200_CSR_WANT_FUSED) && num_edges > 0 && g->d_desc) {
+    walk_b200_csr csr{};
+    csr.rowptr = g->d_rowptr; csr.col = g->d_col; csr.num_nodes = num_nodes; csr.num_edges = num_edges;
+    csr.rowdesc = g->d_desc;
+    G_TRY(cudaMalloc(&g->d_fused, (size_t)num_edges * 16));
+    if (int rc = walk_b200_fused_build(&csr, g->d_fused, g->d_flags, s)) return bail(rc);
+    G_TRY(cudaMemcpyAsync(&f, g->d_flags, 4, cudaMemcpyDeviceToHost, s));
+    G_TRY(cudaStreamSynchronize(s));
+    if (f) { flags_to_status(f); return bail(fail(WALK_B200_ERR_CSR_INVALID, "fused record build failed: %s", std::string(g_last_error).c_str())); }
   }
   G_TRY(cudaStreamSynchronize(s));
 #undef G_TRY
@@ -815,6 +904,8 @@ int walk_b200_graph_destroy(walk_b200_graph* g) {
     if (g->d_col) cudaFree(g->d_col);
     if (g->d_desc) cudaFree(g->d_desc);
     if (g->d_edgeset) cudaFree(g->d_edgeset);
+    if (g->d_revpos) cudaFree(g->d_revpos);
+    if (g->d_fused) cudaFree(g->d_fused);
     if (g->d_flags) cudaFree(g->d_flags);
   }
   delete g;
@@ -827,13 +918,16 @@ int walk_b200_graph_csr(const walk_b200_graph* g, walk_b200_csr* out) {
   out->rowptr = g->d_rowptr; out->col = g->d_col; out->num_nodes = g->num_nodes; out->num_edges = g->num_edges;
   out->rowdesc = g->d_desc; out->flags = g->csr_flags;
   out->edgeset = g->d_edgeset; out->edgeset_buckets = g->edgeset_buckets;
+  out->revpos = g->d_revpos;
+  out->fused = g->d_fused;
   return WALK_B200_OK;
 }
 
 int walk_b200_graph_device_bytes(const walk_b200_graph* g, int64_t* bytes) {
   if (!g || !bytes) return fail(WALK_B200_ERR_INVALID_ARG, "graph or bytes is NULL");
   *bytes = (g->num_nodes + 1) * 8 + g->num_edges * 8 + (g->d_desc ? g->num_nodes * 8 : 0) +
-           (int64_t)(g->d_edgeset ? g->edgeset_buckets * kEdgeSlotsPerBucket * 8 : 0);
+           (int64_t)(g->d_edgeset ? g->edgeset_buckets * kEdgeSlotsPerBucket * 8 : 0) +
+           (g->d_revpos ? g->num_edges * 4 : 0) + (g->d_fused ? g->num_edges * 16 : 0);
   return WALK_B200_OK;
 }
 

@@ -43,6 +43,10 @@ struct L2Policy {
 
 __device__ __forceinline__ L2Policy make_policies(int hints) {
   L2Policy p;
+  if (hints & 4) {  // no explicit policy at all (0 selects the plain load forms below)
+    p.keep = p.stream = p.normal = 0;
+    return p;
+  }
   asm("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p.normal));
   p.keep = p.normal;
   p.stream = p.normal;
@@ -56,21 +60,25 @@ __device__ __forceinline__ L2Policy make_policies(int hints) {
 // 64-byte prefetch size halves that (measured: 123 -> 63 bytes of DRAM per gather).
 __device__ __forceinline__ int64_t ld8(const void* addr, uint64_t policy) {
   int64_t v;
-  asm("ld.global.nc.L2::cache_hint.L2::64B.b64 %0, [%1], %2;" : "=l"(v) : "l"(addr), "l"(policy));
+  if (policy) asm("ld.global.nc.L2::cache_hint.L2::64B.b64 %0, [%1], %2;" : "=l"(v) : "l"(addr), "l"(policy));
+  else asm("ld.global.nc.L2::64B.b64 %0, [%1];" : "=l"(v) : "l"(addr));
   return v;
 }
 __device__ __forceinline__ uint32_t ld4(const void* addr, uint64_t policy) {
   uint32_t v;
-  asm("ld.global.nc.L2::cache_hint.b32 %0, [%1], %2;" : "=r"(v) : "l"(addr), "l"(policy));
+  if (policy) asm("ld.global.nc.L2::cache_hint.b32 %0, [%1], %2;" : "=r"(v) : "l"(addr), "l"(policy));
+  else asm("ld.global.nc.b32 %0, [%1];" : "=r"(v) : "l"(addr));
   return v;
 }
 __device__ __forceinline__ ulonglong2 ld16(const void* addr, uint64_t policy) {
   ulonglong2 v;
-  asm("ld.global.nc.L2::cache_hint.L2::64B.v2.b64 {%0, %1}, [%2], %3;" : "=l"(v.x), "=l"(v.y) : "l"(addr), "l"(policy));
+  if (policy) asm("ld.global.nc.L2::cache_hint.L2::64B.v2.b64 {%0, %1}, [%2], %3;" : "=l"(v.x), "=l"(v.y) : "l"(addr), "l"(policy));
+  else asm("ld.global.nc.L2::64B.v2.b64 {%0, %1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(addr));
   return v;
 }
 __device__ __forceinline__ void st8(void* addr, int64_t v, uint64_t policy) {
-  asm volatile("st.global.L2::cache_hint.b64 [%0], %1, %2;" ::"l"(addr), "l"(v), "l"(policy) : "memory");
+  if (policy) asm volatile("st.global.L2::cache_hint.b64 [%0], %1, %2;" ::"l"(addr), "l"(v), "l"(policy) : "memory");
+  else asm volatile("st.global.b64 [%0], %1;" ::"l"(addr), "l"(v) : "memory");
 }
 
 // Row bounds of node v: one 8-byte load when a packed descriptor exists.
@@ -181,10 +189,33 @@ __global__ void __launch_bounds__(kBlock) csr_validate_kernel(const int64_t* __r
 // ---------------------------------------------------------------------------------
 // uniform walk
 // ---------------------------------------------------------------------------------
+// fused edge records: fused[e] = (col[e], row descriptor of col[e]). One 16-byte gather then
+// yields the next node *and* its row bounds, so a uniform step is one dependent DRAM access
+// instead of two (col entry, then the target's row descriptor).
+__global__ void __launch_bounds__(kBlock) fused_build_kernel(const int64_t* __restrict__ col,
+                                                             const uint64_t* __restrict__ desc,
+                                                             int64_t num_nodes, int64_t num_edges,
+                                                             ulonglong2* __restrict__ fused, uint32_t* flags) {
+  const int64_t stride = (int64_t)gridDim.x * kBlock;
+  for (int64_t e = (int64_t)blockIdx.x * kBlock + threadIdx.x; e < num_edges; e += stride) {
+    const int64_t c = col[e];
+    ulonglong2 rec;
+    rec.x = (unsigned long long)c;
+    if ((uint64_t)c >= (uint64_t)num_nodes) {
+      raise_flag(flags, WALK_B200_FLAG_BAD_NODE);
+      rec.y = 0;  // degree 0: a walk that lands here parks
+    } else {
+      rec.y = __ldg(desc + c);
+    }
+    fused[e] = rec;
+  }
+}
+
 struct UniformParams {
   const int64_t* rowptr;
   const int64_t* col;
   const uint64_t* desc;
+  const ulonglong2* fused;
   int64_t num_nodes, num_edges;
   const int64_t* start;
   const float* rand;
@@ -225,6 +256,32 @@ __device__ __forceinline__ int64_t uniform_step(const UniformParams& P, const L2
   return e;
 }
 
+// Same step on fused edge records: the lane carries the row bounds of `cur` and gets the next
+// node together with that node's bounds from one 16-byte gather.
+__device__ __forceinline__ int64_t uniform_step_fused(const UniformParams& P, const L2Policy& pol, int64_t& cur,
+                                                      int64_t& rs, int64_t& deg, bool& parked, float r) {
+  if (deg <= 0) {
+    parked = true;
+    return -1;
+  }
+  const float prod = __fmul_rn(r, __ll2float_rn(deg));
+  int64_t e = rs + __float2ll_rz(prod);
+  if ((uint64_t)e >= (uint64_t)P.num_edges) {
+    raise_flag(P.flags, WALK_B200_FLAG_BAD_EDGE);
+    e = e < 0 ? 0 : P.num_edges - 1;
+  }
+  const ulonglong2 rec = ld16(P.fused + e, pol.stream);
+  if (rec.x >= (uint64_t)P.num_nodes) {
+    raise_flag(P.flags, WALK_B200_FLAG_BAD_NODE);  // park: keep cur
+    parked = true;
+  } else {
+    cur = (int64_t)rec.x;
+    rs = (int64_t)(rec.y & kDescStartMask);
+    deg = (int64_t)(rec.y >> kDescStartBits);
+  }
+  return e;
+}
+
 // Plain variant: every thread reads its own rand entries and writes its own row with
 // 8-byte strided accesses. Kept as the baseline the staged kernel is measured against
 // (it is what the reference's Metal kernel does) and for walk lengths below one chunk.
@@ -258,8 +315,9 @@ __global__ void __launch_bounds__(kBlock) uniform_walk_direct_kernel(const Unifo
 // segments of S consecutive int64. Global traffic on both sides is whole sectors; the
 // only divergent accesses left per step are the row fetch and the col gather. The next
 // chunk's rand is prefetched into registers while the current chunk walks.
-template <int S, int MIN_BLOCKS, bool USE_DESC, bool HAS_EOUT>
+template <int S, int MIN_BLOCKS, bool USE_DESC, bool HAS_EOUT, bool FUSED = false>
 __global__ void __launch_bounds__(kBlock, MIN_BLOCKS) uniform_walk_staged_kernel(const UniformParams P) {
+  static_assert(!FUSED || USE_DESC, "fused edge records carry row descriptors");
   constexpr int kPitch = 33;  // 8-byte slots per tile row: 32 lanes + 1 pad
   __shared__ unsigned long long tiles[kWarpsPerBlock][S][kPitch];
   const int lane = threadIdx.x & 31;
@@ -274,6 +332,7 @@ __global__ void __launch_bounds__(kBlock, MIN_BLOCKS) uniform_walk_staged_kernel
   const int64_t w = w0 + lane;
 
   int64_t cur = 0;
+  int64_t cur_rs = 0, cur_deg = 0;  // FUSED: row bounds of cur travel with the lane
   bool parked = !live;
   if (live) {
     cur = P.start[w];
@@ -281,6 +340,8 @@ __global__ void __launch_bounds__(kBlock, MIN_BLOCKS) uniform_walk_staged_kernel
     if ((uint64_t)cur >= (uint64_t)P.num_nodes) {
       raise_flag(P.flags, WALK_B200_FLAG_BAD_NODE);
       parked = true;
+    } else if (FUSED) {
+      load_row<true>(P.rowptr, P.desc, cur, pol.keep, cur_rs, cur_deg);
     }
   }
 
@@ -324,7 +385,11 @@ __global__ void __launch_bounds__(kBlock, MIN_BLOCKS) uniform_walk_staged_kernel
     if (live) {
       for (int j = 0; j < sc; j++) {
         int64_t e = -1;
-        if (!parked) e = uniform_step<USE_DESC>(P, pol, cur, parked, __uint_as_float((uint32_t)tile[j][lane]));
+        if (!parked) {
+          const float r = __uint_as_float((uint32_t)tile[j][lane]);
+          e = FUSED ? uniform_step_fused(P, pol, cur, cur_rs, cur_deg, parked, r)
+                    : uniform_step<USE_DESC>(P, pol, cur, parked, r);
+        }
         tile[j][lane] = (unsigned long long)cur;
         if (HAS_EOUT) eout_span[(int64_t)lane * L + l0 + j] = e;
       }
@@ -396,6 +461,46 @@ __global__ void __launch_bounds__(kBlock) edgeset_build_kernel(const int64_t* __
 }
 
 // ---------------------------------------------------------------------------------
+// reverse positions: revpos[e] for edge e = (u -> v) is the index in col of (v -> u)
+// ---------------------------------------------------------------------------------
+// With it a node2vec step knows, without touching col, whether a drawn edge leads back to
+// the previous node. Needs rows strictly ascending (binary search, and "x == t" must mean
+// "this very edge"); a violation raises WALK_B200_FLAG_UNSORTED_ROW and the array must not
+// be used. kNoEdge marks edges without a reverse.
+constexpr uint32_t kNoEdge = 0xffffffffu;       // the reverse edge does not exist
+constexpr uint32_t kUnknownEdge = 0xfffffffeu;  // not looked up: the shortcut must not be taken
+
+__global__ void __launch_bounds__(kBlock) revpos_build_kernel(const int64_t* __restrict__ rowptr,
+                                                              const int64_t* __restrict__ col,
+                                                              int64_t num_nodes, int64_t num_edges,
+                                                              uint32_t* __restrict__ revpos, uint32_t* flags) {
+  const int64_t stride = (int64_t)gridDim.x * kBlock;
+  for (int64_t e = (int64_t)blockIdx.x * kBlock + threadIdx.x; e < num_edges; e += stride) {
+    int64_t lo = 0, hi = num_nodes;  // source row u of edge e: last u with rowptr[u] <= e
+    while (hi - lo > 1) {
+      const int64_t mid = lo + (hi - lo) / 2;
+      if (__ldg(rowptr + mid) <= e) lo = mid; else hi = mid;
+    }
+    const int64_t u = lo;
+    const int64_t v = __ldg(col + e);
+    uint32_t pos = kNoEdge;
+    if ((uint64_t)v >= (uint64_t)num_nodes) {
+      raise_flag(flags, WALK_B200_FLAG_BAD_NODE);
+    } else {
+      if (e > __ldg(rowptr + u) && __ldg(col + e - 1) >= v) raise_flag(flags, WALK_B200_FLAG_UNSORTED_ROW);
+      int64_t a = __ldg(rowptr + v), b = __ldg(rowptr + v + 1);
+      while (a < b) {
+        const int64_t mid = a + (b - a) / 2;
+        const int64_t w = __ldg(col + mid);
+        if (w == u) { pos = (uint32_t)mid; break; }
+        if (w < u) a = mid + 1; else b = mid;
+      }
+    }
+    revpos[e] = pos;
+  }
+}
+
+// ---------------------------------------------------------------------------------
 // node2vec walk
 // ---------------------------------------------------------------------------------
 struct Node2vecParams {
@@ -404,6 +509,7 @@ struct Node2vecParams {
   const uint64_t* desc;
   const uint64_t* edgeset;
   uint64_t edgeset_buckets;
+  const uint32_t* revpos;
   int64_t num_nodes, num_edges;
   const int64_t* start;
   int64_t num_walks;
@@ -444,8 +550,16 @@ enum : int { MEMBER_SEARCH_PREV = 0, MEMBER_SEARCH_CAND = 1, MEMBER_HASH = 2 };
 // the candidate x in the previous node's sorted row; MEMBER_SEARCH_CAND searches the
 // previous node t in the candidate's row, as the reference's is_neighbor(x, t) does;
 // MEMBER_HASH asks the edge hash set for (x -> t).
-template <typename idx_t, int MEMBER, bool USE_DESC, bool HAS_EOUT, bool COUNT>
+//
+// REV (with MEMBER_HASH, row descriptors and 32-bit indices): the lane also carries ret_e, the
+// index in col of the edge back to the previous node (one 4-byte revpos load riding along with
+// the row fetch). An attempt whose drawn edge is ret_e knows its candidate (x = t) without a
+// gather, and an attempt whose accept draw is >= cut1 can only be accepted by the return rule:
+// if its edge is not ret_e it is rejected without touching memory at all. At (p, q) = (0.25, 4)
+// that is three attempts in four. Same draws, same decisions, fewer gathers.
+template <typename idx_t, int MEMBER, bool USE_DESC, bool HAS_EOUT, bool COUNT, bool REV = false>
 __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(const Node2vecParams P) {
+  static_assert(!REV || (MEMBER == MEMBER_HASH && USE_DESC && sizeof(idx_t) == 4), "REV needs hash membership, row descriptors, 32-bit indices");
   constexpr unsigned kFull = 0xffffffffu;
   const int lane = threadIdx.x & 31;
   const L2Policy pol = make_policies(P.hints);
@@ -469,6 +583,7 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
   using uidx_t = typename std::conditional<sizeof(idx_t) == 4, uint32_t, uint64_t>::type;
   uidx_t lo = 0, hi = 0;          // search window / hash bucket + probe count / parked accept draw
   idx_t e = 0;                    // sampled edge index
+  idx_t ret_e = (idx_t)kUnknownEdge;  // REV: index of the edge v -> t (kNoEdge: there is none)
   int32_t l = 0;                  // step being produced
   uint32_t a = 0;                 // attempt counter of this step
   int state = ST_IDLE;
@@ -505,6 +620,9 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
       int64_t* out = P.n_out + i * ((int64_t)L + 1);
       int64_t* eout = HAS_EOUT ? P.e_out + i * (int64_t)L : nullptr;
 
+      bool accept = false, reject = false;
+      bool need_load = true;  // REV: some attempts are decided without touching memory
+
       // ---- address of this trip's gather
       const void* addr;
       uint64_t policy = pol.stream;
@@ -523,6 +641,28 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
           lo = acc;  // parked until the candidate arrives
         }
         addr = col + (int64_t)e;
+        if (REV && l > 0 && ret_e != (idx_t)kUnknownEdge) {
+          const bool is_ret = (e == ret_e);
+          if (v_deg == 1) {
+            if (is_ret) { x = t; accept = true; need_load = false; }
+          } else {
+            const uint32_t acc = (uint32_t)lo;
+            if (is_ret) {  // the candidate is the previous node: no gather needed to know it
+              need_load = false;
+              x = t;
+              if (COUNT) c_attempts++;
+              if (acc < P.cut2 || acc < P.cut0) accept = true;
+              else if (acc < P.cut1) {  // only a self-loop t -> t could still accept: ask the edge set
+                if (COUNT) { c_member++; state = ST_XROW; }
+                else { lo = (uidx_t)edge_bucket(edge_key((uint64_t)x, (uint64_t)t), P.edgeset_buckets); hi = 0; state = ST_HASH; }
+              } else reject = true;
+            } else if (acc >= P.cut2 && acc >= P.cut1) {  // not the way back and too large for the other rules
+              need_load = false;
+              if (COUNT) c_attempts++;
+              reject = true;
+            }
+          }
+        }
       } else if (state == ST_XROW) {
         addr = USE_DESC ? (const void*)(P.desc + (int64_t)x) : (const void*)(P.rowptr + (int64_t)x);
         policy = pol.keep;
@@ -534,8 +674,11 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
       }
 
       int64_t val = 0, val2 = 0;
+      uint32_t rev = kUnknownEdge;
       ulonglong2 h0 = {0, 0}, h1 = {0, 0};
-      if (MEMBER == MEMBER_HASH && state == ST_HASH) {
+      if (!need_load) {
+        // decided above
+      } else if (MEMBER == MEMBER_HASH && state == ST_HASH) {
         h0 = ld16(addr, policy);
         h1 = ld16((const char*)addr + 16, policy);
         if (COUNT) c_loads += 4;
@@ -546,11 +689,16 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
         // the instrumented kernel's extra look at deg(x) is bookkeeping, not part of the walk
         const bool bookkeeping = COUNT && state == ST_XROW && MEMBER != MEMBER_SEARCH_CAND;
         if (COUNT && !bookkeeping) c_loads += pair ? 2 : 1;
+        if (REV && state == ST_ROW && l > 0 && e != (idx_t)kUnknownEdge) {
+          rev = ld4(P.revpos + (int64_t)e, policy);
+          if (COUNT) c_loads += 1;
+        }
       }
 
       // ---- consume it
-      bool accept = false, reject = false;
-      if (state == ST_START) {
+      if (!need_load) {
+        // nothing was loaded
+      } else if (state == ST_START) {
         out[0] = val;
         t = (idx_t)val;
         v = (idx_t)val;
@@ -578,6 +726,7 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
             v_re = (idx_t)(rs + deg);
             v_deg = deg > 0x7fffffffll ? 0x80000000u : (uint32_t)deg;
             a = 0;
+            if (REV) ret_e = (idx_t)rev;
             state = ST_ATTEMPT;
             if (COUNT) { if (l == 0) c_first++; else if (deg == 1) c_deg1++; else c_sampled++; }
           }
@@ -652,6 +801,7 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
         if (a >= P.max_attempts) {
           raise_flag(P.flags, WALK_B200_FLAG_ATTEMPT_CAP);
           x = v; accept = true;  // give up on this step: stand still
+          if (REV) e = (idx_t)kUnknownEdge;
         }
       }
       if (accept) {

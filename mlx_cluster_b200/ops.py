@@ -58,7 +58,8 @@ class WalkGraph:
     row start | degree << 36) so that a walk step fetches row bounds with one load."""
 
     def __init__(self, rowptr: torch.Tensor, col: torch.Tensor, *, symmetric: bool = False,
-                 use_rowdesc: bool = True, edgeset: bool = False, validate: bool = False, stream=None):
+                 use_rowdesc: bool = True, edgeset: bool = False, fused: bool = False, validate: bool = False,
+                 stream=None):
         if not rowptr.is_cuda:
             raise ValueError("WalkGraph needs CUDA tensors (use HostGraph for host arrays)")
         dev = rowptr.device
@@ -73,6 +74,8 @@ class WalkGraph:
         self.rowdesc = None
         self.edgeset = None
         self.edgeset_buckets = 0
+        self.revpos = None
+        self.fused = None
         self._version = (rowptr._version, col._version)
         with torch.cuda.device(dev):
             self.flags = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -92,6 +95,24 @@ class WalkGraph:
                 self.flags.zero_()
             if edgeset and self.num_edges > 0:
                 self.build_edgeset(stream=stream)
+            if fused and self.num_edges > 0:
+                self.build_fused(stream=stream)
+
+    def build_fused(self, stream=None):
+        """Build the fused edge records (16 bytes per edge: target node + its row descriptor) that
+        make a uniform walk step one gather instead of two."""
+        if self.fused is not None or self.rowdesc is None:
+            return
+        with torch.cuda.device(self.device):
+            rec = torch.empty((self.num_edges, 2), dtype=torch.int64, device=self.device)
+            csr = self.csr()
+            _lib.check(_lib.lib().walk_b200_fused_build(C.byref(csr), rec.data_ptr(), self.flags.data_ptr(),
+                                                        _stream_handle(stream, self.device)))
+            f = int(self.flags.item())
+            self.flags.zero_()
+            if f:
+                raise ValueError(f"fused record build failed, status flags 0x{f:x}: {describe_flags(f)}")
+            self.fused = rec
 
     def build_edgeset(self, stream=None):
         """Build the edge hash set (16 bytes per edge) that turns node2vec's membership test
@@ -109,11 +130,20 @@ class WalkGraph:
             if f:
                 raise ValueError(f"edge set build failed, status flags 0x{f:x}: {describe_flags(f)}")
             self.edgeset, self.edgeset_buckets = table, buckets
+            # reverse positions ride along when they can be built (rows strictly ascending, < 2^32 - 2 edges)
+            if self.num_edges < 2**32 - 2 and self.rowdesc is not None:
+                rev = torch.empty(self.num_edges, dtype=torch.int32, device=self.device)
+                _lib.check(_lib.lib().walk_b200_revpos_build(C.byref(csr), rev.data_ptr(), self.flags.data_ptr(),
+                                                             _stream_handle(stream, self.device)))
+                f = int(self.flags.item())
+                self.flags.zero_()
+                if not f:
+                    self.revpos = rev
 
     def csr(self) -> _lib.Csr:
         return _lib.Csr(self.rowptr.data_ptr(), _ptr(self.col), self.num_nodes, self.num_edges,
                         _ptr(self.rowdesc), _lib.CSR_SYMMETRIC if self.symmetric else 0, 0,
-                        _ptr(self.edgeset), self.edgeset_buckets)
+                        _ptr(self.edgeset), self.edgeset_buckets, _ptr(self.revpos), _ptr(self.fused))
 
     def validate(self, start: Optional[torch.Tensor] = None, *, check_sorted: bool = True, stream=None):
         """Raise ValueError when the CSR (and, if given, the start nodes) is malformed."""
@@ -154,15 +184,17 @@ def _key(rowptr, col, symmetric):
             str(rowptr.device), bool(symmetric))
 
 
-def prepare_graph(rowptr, col, *, symmetric: bool = False, edgeset: bool = False,
+def prepare_graph(rowptr, col, *, symmetric: bool = False, edgeset: bool = False, fused: bool = False,
                   validate: bool = False) -> "WalkGraph":
     """Build (or fetch from a small cache) the device-side graph for these CSR tensors."""
     k = _key(rowptr, col, symmetric)
     g = _GRAPH_CACHE.get(k)
     if g is not None and edgeset:
         g.build_edgeset()
+    if g is not None and fused:
+        g.build_fused()
     if g is None:
-        g = WalkGraph(rowptr, col, symmetric=symmetric, edgeset=edgeset, validate=validate)
+        g = WalkGraph(rowptr, col, symmetric=symmetric, edgeset=edgeset, fused=fused, validate=validate)
         _GRAPH_CACHE[k] = g
         while len(_GRAPH_CACHE) > _CACHE_SIZE:
             _GRAPH_CACHE.popitem(last=False)
@@ -174,8 +206,8 @@ def prepare_graph(rowptr, col, *, symmetric: bool = False, edgeset: bool = False
 class HostGraph:
     """A CSR graph given as host arrays, uploaded once and kept resident on one device."""
 
-    def __init__(self, rowptr, col, *, symmetric: bool = False, edgeset: bool = False, validate: bool = False,
-                 device=None):
+    def __init__(self, rowptr, col, *, symmetric: bool = False, edgeset: bool = False, fused: bool = False,
+                 validate: bool = False, device=None):
         self.rowptr = _require(_as_cpu_tensor(rowptr), "rowptr", torch.int64)
         self.col = _require(_as_cpu_tensor(col), "col", torch.int64)
         self.num_nodes = self.rowptr.numel() - 1
@@ -185,7 +217,8 @@ class HostGraph:
         with torch.cuda.device(self.device):
             _lib.check(_lib.lib().walk_b200_graph_create(
                 self.rowptr.data_ptr(), _ptr(self.col), self.num_nodes, self.num_edges,
-                (_lib.CSR_SYMMETRIC if symmetric else 0) | (_lib.CSR_WANT_EDGESET if edgeset else 0),
+                (_lib.CSR_SYMMETRIC if symmetric else 0) | (_lib.CSR_WANT_EDGESET if edgeset else 0)
+                | (_lib.CSR_WANT_FUSED if fused else 0),
                 int(validate), C.byref(h)))
         self._h = h
 
@@ -212,11 +245,11 @@ def _as_cpu_tensor(a):
     return torch.from_numpy(np.ascontiguousarray(a))
 
 
-def _host_graph(rowptr, col, symmetric, validate, edgeset=False):
-    k = _key(rowptr, col, symmetric) + (bool(edgeset),)
+def _host_graph(rowptr, col, symmetric, validate, edgeset=False, fused=False):
+    k = _key(rowptr, col, symmetric) + (bool(edgeset), bool(fused))
     g = _HOST_CACHE.get(k)
     if g is None:
-        g = HostGraph(rowptr, col, symmetric=symmetric, edgeset=edgeset, validate=validate)
+        g = HostGraph(rowptr, col, symmetric=symmetric, edgeset=edgeset, fused=fused, validate=validate)
         _HOST_CACHE[k] = g
         while len(_HOST_CACHE) > _CACHE_SIZE:
             _, old = _HOST_CACHE.popitem(last=False)
@@ -251,7 +284,8 @@ def _finish(graph, out, e_out, check, return_edges):
 
 
 def random_walk(rowptr, col, start, rand, walk_length, *, stream=None, return_edges: bool = False,
-                check: bool = False, out: Optional[torch.Tensor] = None, graph: Optional[WalkGraph] = None):
+                check: bool = False, out: Optional[torch.Tensor] = None, graph: Optional[WalkGraph] = None,
+                fused: bool = False):
     """Uniform CSR random walk (``random_walk`` of the reference, ``bindings.cpp:12-21``).
 
     Step ``l`` of walk ``w`` moves from ``v`` to ``col[rowptr[v] + int(rand[w, l] * deg(v))]``
@@ -261,14 +295,16 @@ def random_walk(rowptr, col, start, rand, walk_length, *, stream=None, return_ed
     Extra keyword-only options (not in the reference): ``return_edges`` also returns the
     edge ids ``[n, walk_length]`` the reference computes but never exposes; ``check``
     synchronises and raises if the kernel met malformed input; ``out`` supplies the output
-    tensor; ``graph`` passes a prepared :class:`WalkGraph` instead of ``rowptr``/``col``.
+    tensor; ``graph`` passes a prepared :class:`WalkGraph` instead of ``rowptr``/``col``;
+    ``fused=True`` builds (once per graph, 16 bytes per edge) fused edge records that make a step
+    one gather instead of two -- worth it when many calls walk the same graph.
     """
     L = _check_walk_length(walk_length)
     if not isinstance(start, torch.Tensor) or not start.is_cuda:
-        return _random_walk_host(rowptr, col, start, rand, L, return_edges, out)
+        return _random_walk_host(rowptr, col, start, rand, L, return_edges, out, fused)
     dev = start.device
     g = graph if graph is not None else prepare_graph(_require(rowptr, "rowptr", torch.int64, dev),
-                                                      _require(col, "col", torch.int64, dev))
+                                                      _require(col, "col", torch.int64, dev), fused=fused)
     _require(start, "start", torch.int64, g.device)
     _require(rand, "rand", torch.float32, g.device)
     n = start.numel()
@@ -351,14 +387,14 @@ def _host_out(n, L, out):
     return out
 
 
-def _random_walk_host(rowptr, col, start, rand, L, return_edges, out):
+def _random_walk_host(rowptr, col, start, rand, L, return_edges, out, fused=False):
     rowptr, col = _as_cpu_tensor(rowptr), _as_cpu_tensor(col)
     start = _require(_as_cpu_tensor(start), "start", torch.int64)
     rand = _require(_as_cpu_tensor(rand), "rand", torch.float32)
     n = start.numel()
     if rand.numel() != n * L:
         raise ValueError(f"rand must hold n * walk_length = {n * L} values, has {rand.numel()}")
-    g = _host_graph(rowptr, col, False, False)
+    g = _host_graph(rowptr, col, False, False, fused=fused)
     out = _host_out(n, L, out)
     e_out = torch.empty((n, L), dtype=torch.int64, pin_memory=True) if return_edges else None
     with torch.cuda.device(g.device):

@@ -25,10 +25,11 @@ def test_host_arrays_uniform_and_biased(cuda, golden):
     out = random_walk(g["rowptr1"], g["col1"], g["start1"], g["rand1"], 5)
     assert not out.is_cuda
     np.testing.assert_array_equal(out.numpy(), g["uniform1_n"])
-    out, e = random_walk(torch.from_numpy(g["rowptr2"]), torch.from_numpy(g["col2"]), torch.from_numpy(g["start2"]),
-                         torch.from_numpy(g["rand2"]), 20, return_edges=True)
-    np.testing.assert_array_equal(out.numpy(), g["uniform2_n"])
-    np.testing.assert_array_equal(e.numpy(), g["uniform2_e"])
+    for fused in (False, True):
+        out, e = random_walk(torch.from_numpy(g["rowptr2"]), torch.from_numpy(g["col2"]), torch.from_numpy(g["start2"]),
+                             torch.from_numpy(g["rand2"]), 20, return_edges=True, fused=fused)
+        np.testing.assert_array_equal(out.numpy(), g["uniform2_n"])
+        np.testing.assert_array_equal(e.numpy(), g["uniform2_e"])
     want = oracle.node2vec_walk(g["rowptr2"], g["col2"], g["start2"], 20, 0.5, 2.0, seed=4)
     for kw in (dict(symmetric=False), dict(symmetric=True), dict(edgeset=True)):
         out = rejection_sampling(g["rowptr2"], g["col2"], g["start2"], 20, 0.5, 2.0, seed=4, **kw)
@@ -81,7 +82,7 @@ def test_host_entry_reports_bad_input(cuda, golden):
     assert hg.device_bytes() == (2709 + 10556 + 2708) * 8
     hg.close()
     hg = HostGraph(g["rowptr1"], g["col1"], edgeset=True)
-    assert hg.device_bytes() == (2709 + 10556 + 2708) * 8 + _lib.edgeset_buckets(10556) * 32
+    assert hg.device_bytes() == (2709 + 10556 + 2708) * 8 + _lib.edgeset_buckets(10556) * 32 + 10556 * 4
     hg.close()
 
 

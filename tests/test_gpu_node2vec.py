@@ -21,12 +21,14 @@ PQS = [(1.0, 1.0), (0.5, 2.0), (4.0, 0.25), (0.25, 4.0), (1.0, 3.0)]
 def _reset_tuning():
     yield
     _lib.set_tuning("n2v_idx", 0)
-    _lib.set_tuning("l2_hints", 1)
+    _lib.set_tuning("n2v_rev", 1)
+    _lib.set_tuning("l2_hints", 3)
 
 
 def run_gpu(dev, rowptr, col, start, L, p, q, *, seed=0, base=0, symmetric=False, rowdesc=True,
-            idx64=False, edges=True, counters=False, edgeset=False):
+            idx64=False, edges=True, counters=False, edgeset=False, rev=True):
     _lib.set_tuning("n2v_idx", 1 if idx64 else 0)
+    _lib.set_tuning("n2v_rev", 2 if rev else 0)
     g = WalkGraph(torch.from_numpy(rowptr).to(dev), torch.from_numpy(col).to(dev), symmetric=symmetric,
                   use_rowdesc=rowdesc, edgeset=edgeset)
     assert (g.edgeset is not None) == (edgeset and col.size > 0)
@@ -38,7 +40,7 @@ def run_gpu(dev, rowptr, col, start, L, p, q, *, seed=0, base=0, symmetric=False
 
 
 MEMBERSHIP = {"search_candidate_row": dict(symmetric=False), "search_previous_row": dict(symmetric=True),
-              "edge_hash_set": dict(edgeset=True)}
+              "edge_hash_set": dict(edgeset=True, rev=False), "edge_hash_set_and_reverse_positions": dict(edgeset=True)}
 
 
 @pytest.mark.parametrize("pq", PQS)
@@ -150,6 +152,27 @@ def test_self_loops_and_degree_one_chains(cuda):
         np.testing.assert_array_equal(run_gpu(cuda, rp, cl, start, 25, 0.25, 4.0, seed=1, symmetric=sym, edges=False), n_o)
 
 
+def test_unsorted_rows_fall_back_to_the_hash_set_alone(cuda):
+    """Rows in arbitrary order: no binary search and no reverse positions, but the edge hash set
+    still answers membership exactly."""
+    rng = np.random.default_rng(5)
+    rowptr, col = random_csr(rng, 400, 6.0, symmetric=True)
+    col = col.copy()
+    for v in range(400):
+        rng.shuffle(col[rowptr[v]:rowptr[v + 1]])
+    start = rng.integers(0, 400, 3000).astype(np.int64)
+    g = WalkGraph(torch.from_numpy(rowptr).to(cuda), torch.from_numpy(col).to(cuda), edgeset=True)
+    assert g.edgeset is not None and g.revpos is None
+    for pq in [(0.25, 4.0), (2.0, 0.5)]:
+        want = oracle.node2vec_walk(rowptr, col, start, 25, *pq, seed=2)
+        got = rejection_sampling(None, None, torch.from_numpy(start).to(cuda), 25, *pq, graph=g, seed=2, check=True)
+        np.testing.assert_array_equal(got.cpu().numpy(), want)
+    sorted_graph = WalkGraph(torch.from_numpy(rowptr).to(cuda),
+                             torch.from_numpy(np.concatenate([np.sort(col[rowptr[v]:rowptr[v + 1]]) for v in range(400)])).to(cuda),
+                             edgeset=True)
+    assert sorted_graph.revpos is not None
+
+
 def test_medium_rmat_stream_exact(cuda):
     rowptr, col = graphs.rmat_csr(14, 16, seed=6, device=cuda)
     n_nodes = rowptr.numel() - 1
@@ -164,8 +187,18 @@ def test_medium_rmat_stream_exact(cuda):
             assert c["attempts"] == cnt["attempts"] and c["membership"] == cnt["membership_needed"]
             assert c["formula_probes"] == cnt["bsearch_probes"]
         hashed = WalkGraph(rowptr, col, edgeset=True)
-        out = rejection_sampling(None, None, start, 40, *pq, graph=hashed, seed=77, check=True)
-        np.testing.assert_array_equal(out.cpu().numpy(), n_o)
+        assert hashed.revpos is not None
+        loads = {}
+        for rev in (1, 0):
+            _lib.set_tuning("n2v_rev", 2 if rev else 0)
+            out, c = rejection_sampling(None, None, start, 40, *pq, graph=hashed, seed=77, check=True,
+                                        return_counters=True)
+            np.testing.assert_array_equal(out.cpu().numpy(), n_o)
+            assert c["attempts"] == cnt["attempts"] and c["membership"] == cnt["membership_needed"]
+            assert c["formula_probes"] == cnt["bsearch_probes"]
+            loads[rev] = c["loads"]
+        if pq == (0.25, 4.0):
+            assert loads[1] < 0.75 * loads[0]  # three attempts in four need no gather
 
 
 @pytest.mark.parametrize("pq", [(1.0, 1.0), (0.5, 2.0), (4.0, 0.25)])
@@ -216,9 +249,12 @@ def test_properties_at_scale(cuda):
     assert torch.equal(out, general)
     hashed = WalkGraph(rowptr, col, edgeset=True)
     assert torch.equal(out, rejection_sampling(None, None, start, L, 0.25, 4.0, graph=hashed, seed=3, check=True))
-    for hints in (0, 1):
+    for hints in (0, 1, 3):
         _lib.set_tuning("l2_hints", hints)
         assert torch.equal(out, rejection_sampling(None, None, start, L, 0.25, 4.0, graph=hashed, seed=3))
+    _lib.set_tuning("n2v_rev", 0)
+    assert torch.equal(out, rejection_sampling(None, None, start, L, 0.25, 4.0, graph=hashed, seed=3))
+    _lib.set_tuning("n2v_rev", 1)
     _lib.set_tuning("n2v_idx", 1)
     assert torch.equal(out, rejection_sampling(rowptr, col, start, L, 0.25, 4.0, seed=3, symmetric=True))
     assert torch.equal(out, rejection_sampling(None, None, start, L, 0.25, 4.0, graph=hashed, seed=3))

@@ -20,12 +20,15 @@ VARIANTS = {"direct": 1, "staged8": 2, "staged16": 3, "staged4": 4, "staged16_40
 def _reset_tuning():
     yield
     _lib.set_tuning("uniform_variant", 0)
+    _lib.set_tuning("uniform_fused", 1)
 
 
-def run_gpu(dev, rowptr, col, start, rand, L, *, variant="staged8", rowdesc=True, edges=True, check=True):
+def run_gpu(dev, rowptr, col, start, rand, L, *, variant="staged8", rowdesc=True, edges=True, check=True,
+            fused=False):
     _lib.set_tuning("uniform_variant", VARIANTS[variant])
-    g = WalkGraph(torch.from_numpy(rowptr).to(dev), torch.from_numpy(col).to(dev), use_rowdesc=rowdesc)
+    g = WalkGraph(torch.from_numpy(rowptr).to(dev), torch.from_numpy(col).to(dev), use_rowdesc=rowdesc, fused=fused)
     assert (g.rowdesc is not None) == (rowdesc and g.num_nodes > 0)
+    assert (g.fused is not None) == (fused and rowdesc and col.size > 0)
     before = _lib.launch_count()
     res = random_walk(None, None, torch.from_numpy(start).to(dev), torch.from_numpy(rand).to(dev), L,
                       graph=g, return_edges=edges, check=check)
@@ -45,6 +48,10 @@ def test_fixture_workloads_bit_exact(cuda, golden, variant, rowdesc):
     np.testing.assert_array_equal(n, g["uniform1_n"])
     np.testing.assert_array_equal(e, g["uniform1_e"])
     n, e = run_gpu(cuda, g["rowptr2"], g["col2"], g["start2"], g["rand2"], 20, variant=variant, rowdesc=rowdesc)
+    np.testing.assert_array_equal(n, g["uniform2_n"])
+    np.testing.assert_array_equal(e, g["uniform2_e"])
+    # fused edge records (one gather per step): same walks
+    n, e = run_gpu(cuda, g["rowptr2"], g["col2"], g["start2"], g["rand2"], 20, variant=variant, rowdesc=rowdesc, fused=True)
     np.testing.assert_array_equal(n, g["uniform2_n"])
     np.testing.assert_array_equal(e, g["uniform2_e"])
 
@@ -85,6 +92,9 @@ def test_ragged_shapes_against_restatement(cuda, variant):
             np.testing.assert_array_equal(e, e_o, err_msg=f"trial {trial}")
             n_only = run_gpu(cuda, rowptr, col, start, rand, L, variant=variant, rowdesc=rowdesc, edges=False)
             np.testing.assert_array_equal(n_only, n_o)
+        n, e = run_gpu(cuda, rowptr, col, start, rand, L, variant=variant, fused=True)
+        np.testing.assert_array_equal(n, n_o, err_msg=f"trial {trial} fused")
+        np.testing.assert_array_equal(e, e_o, err_msg=f"trial {trial} fused")
 
 
 def test_hub_degree_float32_rounding(cuda):
@@ -98,9 +108,10 @@ def test_hub_degree_float32_rounding(cuda):
     start = np.zeros(6, dtype=np.int64)
     n_o, e_o = oracle.uniform_walk(rowptr, col, start, rand, 1, return_edges=True)
     for variant in ("direct", "staged8"):
-        n, e = run_gpu(cuda, rowptr, col, start, rand, 1, variant=variant)
-        np.testing.assert_array_equal(e, e_o)
-        np.testing.assert_array_equal(n, n_o)
+        for fused in (False, True):
+            n, e = run_gpu(cuda, rowptr, col, start, rand, 1, variant=variant, fused=fused)
+            np.testing.assert_array_equal(e, e_o)
+            np.testing.assert_array_equal(n, n_o)
 
 
 def test_medium_rmat_against_restatement_and_reference(cuda):
@@ -113,6 +124,7 @@ def test_medium_rmat_against_restatement_and_reference(cuda):
     out = random_walk(rowptr, col, start, rand, L, check=True).cpu().numpy()
     args = (rowptr.cpu().numpy(), col.cpu().numpy(), start.cpu().numpy(), rand.cpu().numpy(), L)
     np.testing.assert_array_equal(out, oracle.uniform_walk(*args))
+    np.testing.assert_array_equal(random_walk(rowptr, col, start, rand, L, check=True, fused=True).cpu().numpy(), out)
     if oracle.have_ref():
         np.testing.assert_array_equal(out, oracle.ref_random_walk(*args))
 
@@ -168,6 +180,9 @@ def test_every_step_follows_an_edge_at_full_length(cuda):
     assert torch.equal(e[moved], want[moved])
     out2 = random_walk(rowptr, col, start, rand, L)
     assert torch.equal(out, out2)
+    fused_graph = WalkGraph(rowptr, col, fused=True)
+    out3, e3 = random_walk(None, None, start, rand, L, graph=fused_graph, return_edges=True, check=True)
+    assert torch.equal(out, out3) and torch.equal(e, e3)
     for v in ("direct", "staged16"):
         _lib.set_tuning("uniform_variant", VARIANTS[v])
         assert torch.equal(out, random_walk(rowptr, col, start, rand, L))
