@@ -237,7 +237,7 @@ def run_reference_arm(args, wl):
     return 0
 
 
-def workload_config(wl, n_nodes, n_edges, gpus, membership=None, edge_records=None):
+def workload_config(wl, n_nodes, n_edges, gpus, membership=None, edge_records=None, rand_source=None):
     c = {"workload": args_workload_name(wl), "graph": f"R-MAT scale {wl['scale']} edge factor {wl['edge_factor']} "
          f"(a,b,c,d)=(0.57,0.19,0.19,0.05) seed {wl['seed']}, symmetrised, deduplicated, no self-loops, int64 CSR",
          "num_nodes": n_nodes, "num_directed_edges": n_edges, "starts": "every node once", "walk_length": wl["L"],
@@ -247,7 +247,7 @@ def workload_config(wl, n_nodes, n_edges, gpus, membership=None, edge_records=No
         c.update(p=wl["p"], q=wl["q"], draws="Philox4x32-10, key=seed, counter=(walk,step,attempt)",
                  membership=membership)
     else:
-        c.update(rand="float32 uniform [0,1) [n, walk_length], caller-supplied", edge_records=edge_records)
+        c.update(rand=rand_source or "float32 uniform [0,1) [n, walk_length], caller-supplied", edge_records=edge_records)
     return c
 
 
@@ -362,8 +362,15 @@ def run_ours(args, wl):
         # 8-byte descriptor instead of the 16-byte row pair; fused records: one 16-byte gather per moving step
         gathered_bytes = rows * 24 + moved * 28 if not args.no_fused else rows * 16 + moved * 28 + stay * 12
 
+        if args.device_rand:
+            # draws generated in the kernel (same walks as feeding the replayed stream; tests check that)
+            rand = None
+            alg_bytes -= 4 * moved
+            gathered_bytes -= 4 * moved
+
         def step():
-            random_walk(None, None, start, rand, L, graph=graph, out=out)
+            random_walk(None, None, start, rand, L, graph=graph, out=out, seed=PHILOX_SEED, walk_index_base=b,
+                        walk_index_stride=stride)
 
     sampler = ClockSampler(dev) if rank == 0 else None
     total_ms, per, timed_launches = time_launches(step, args.steps, args.warmup, stream, sampler, barrier)
@@ -399,7 +406,7 @@ def run_ours(args, wl):
 
     # ---- end to end: host buffers through the public API, copies inside the timed region
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and not (wl["kind"] == "uniform" and args.device_rand):
         e2e_steps = max(1, min(args.steps, args.e2e_steps))
         h_rowptr, h_col = rowptr.cpu(), col.cpu()
         h_start = start.cpu().pin_memory()
@@ -455,7 +462,8 @@ def run_ours(args, wl):
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
             "config": workload_config(wl, n_nodes, n_edges, world, args.membership,
-                                      "col + row descriptors" if args.no_fused else "fused 16-byte records"),
+                                      "col + row descriptors" if args.no_fused else "fused 16-byte records",
+                                      "generated in the kernel (Philox4x32-10)" if args.device_rand else None),
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": e2e, "gpu_launches": int(timed_launches), "clocks": clocks, "graph_build_s": build_s,
             "graph_prepare_s_once": prep_s,
@@ -478,6 +486,8 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target CPU time of the cpu_baseline sample")
     ap.add_argument("--membership", default="hash", choices=["hash", "search"],
                     help="node2vec membership test: edge hash set (built once per graph) or binary search over col")
+    ap.add_argument("--device-rand", action="store_true",
+                    help="uniform walk: generate the draws in the kernel instead of reading a rand array")
     ap.add_argument("--no-fused", action="store_true", help="uniform walk: do not build fused edge records")
     ap.add_argument("--no-probe", action="store_true", help="skip the random-gather ceiling probe")
     ap.add_argument("--no-e2e", action="store_true")

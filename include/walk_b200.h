@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define WALK_B200_ABI_VERSION 5
+#define WALK_B200_ABI_VERSION 6
 
 /* ---- return codes ---- */
 #define WALK_B200_OK 0
@@ -110,6 +110,23 @@ uint64_t walk_b200_launch_count(void);
 int walk_b200_uniform_walk(const walk_b200_csr* g, const int64_t* start, const float* rand,
                            int64_t num_walks, int32_t walk_length, int64_t* n_out,
                            int64_t* e_out, uint32_t* status_flags, void* stream);
+
+/*
+ * The same uniform walk with its draws generated in the kernel instead of read from a caller's
+ * rand array (the reference always takes rand_data from the caller, tests/test_random_walk.py:31;
+ * this variant removes that [n, L] float32 input, 4 bytes per step of reads and, on the largest
+ * workloads, an array bigger than the GPU). Draw of step l of global walk w (= walk_index_base +
+ * row * walk_index_stride): Philox4x32-10, key = seed, counter = (w lo32, l >> 2, 0x554E4946, w hi32),
+ * word (l & 3), r = (word >> 8) * 2^-24. walk_b200_uniform_draws fills the matching rand array on
+ * the host, so the result equals walk_b200_uniform_walk on that array bit for bit.
+ */
+int walk_b200_uniform_walk_philox(const walk_b200_csr* g, const int64_t* start, int64_t num_walks,
+                                  int32_t walk_length, uint64_t seed, uint64_t walk_index_base,
+                                  uint64_t walk_index_stride, int64_t* n_out, int64_t* e_out,
+                                  uint32_t* status_flags, void* stream);
+void walk_b200_uniform_draw(uint64_t seed, uint64_t walk, uint32_t step, float* r);
+void walk_b200_uniform_draws(uint64_t seed, uint64_t walk_index_base, uint64_t walk_index_stride,
+                             int64_t num_walks, int32_t walk_length, float* out);
 
 /*
  * node2vec biased walk by rejection sampling. Replaces BiasedRandomWalk::eval_cpu

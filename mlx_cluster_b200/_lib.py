@@ -22,7 +22,8 @@ COUNTER_NAMES = ("loads", "attempts", "membership", "probes",
 # every symbol include/walk_b200.h declares
 EXPORTS = (
     "walk_b200_abi_version", "walk_b200_last_error", "walk_b200_launch_count",
-    "walk_b200_uniform_walk", "walk_b200_node2vec_walk", "walk_b200_rowdesc_pack",
+    "walk_b200_uniform_walk", "walk_b200_uniform_walk_philox", "walk_b200_uniform_draw",
+    "walk_b200_uniform_draws", "walk_b200_node2vec_walk", "walk_b200_rowdesc_pack",
     "walk_b200_csr_validate", "walk_b200_edgeset_buckets", "walk_b200_edgeset_build", "walk_b200_revpos_build", "walk_b200_fused_build", "walk_b200_philox4x32_10", "walk_b200_node2vec_draw",
     "walk_b200_node2vec_thresholds", "walk_b200_shard_range", "walk_b200_shard_count_cyclic",
     "walk_b200_graph_create", "walk_b200_graph_destroy", "walk_b200_graph_csr",
@@ -64,6 +65,11 @@ def lib():
     L.walk_b200_last_error.restype = C.c_char_p
     L.walk_b200_launch_count.restype = u64
     L.walk_b200_uniform_walk.argtypes = [C.POINTER(Csr), vp, vp, i64, i32, vp, vp, vp, vp]
+    L.walk_b200_uniform_walk_philox.argtypes = [C.POINTER(Csr), vp, i64, i32, u64, u64, u64, vp, vp, vp, vp]
+    L.walk_b200_uniform_draw.argtypes = [u64, u64, u32, C.POINTER(C.c_float)]
+    L.walk_b200_uniform_draw.restype = None
+    L.walk_b200_uniform_draws.argtypes = [u64, u64, u64, i64, i32, vp]
+    L.walk_b200_uniform_draws.restype = None
     L.walk_b200_node2vec_walk.argtypes = [C.POINTER(Csr), vp, i64, i32, dbl, dbl, u64, u64, u64, vp, vp, vp, vp, vp]
     L.walk_b200_rowdesc_pack.argtypes = [vp, i64, i64, vp, vp, vp]
     L.walk_b200_csr_validate.argtypes = [C.POINTER(Csr), vp, i64, i32, vp, vp]
@@ -128,6 +134,14 @@ def node2vec_draw(seed: int, walk: int, step: int, attempt: int):
     c, a = C.c_uint32(0), C.c_uint32(0)
     lib().walk_b200_node2vec_draw(seed, walk, step, attempt, C.byref(c), C.byref(a))
     return int(c.value), int(a.value)
+
+
+def uniform_draws(seed: int, num_walks: int, walk_length: int, walk_index_base: int = 0, walk_index_stride: int = 1):
+    """The float32 [num_walks, walk_length] draws the kernel generates for these walks (host replay)."""
+    import numpy as np
+    out = np.empty((num_walks, walk_length), dtype=np.float32)
+    lib().walk_b200_uniform_draws(seed, walk_index_base, walk_index_stride, num_walks, walk_length, out.ctypes.data)
+    return out
 
 
 def node2vec_thresholds(p: float, q: float):

@@ -42,4 +42,17 @@ __host__ __device__ __forceinline__ void node2vec_draw(uint32_t k0, uint32_t k1,
   acc31 = o.y >> 1;
 }
 
+// Draws of the uniform walk when the caller supplies no rand array: one Philox block serves four
+// consecutive steps. counter = (walk lo32, step >> 2, kUniformTag, walk hi32), word (step & 3),
+// r = (word >> 8) * 2^-24: a float32 in [0, 1), never 1.
+constexpr uint32_t kUniformTag = 0x554E4946u;
+
+__host__ __device__ __forceinline__ Philox4 uniform_block(uint32_t k0, uint32_t k1, uint64_t walk, uint32_t step_quad) {
+  return philox4x32_10((uint32_t)walk, step_quad, kUniformTag, (uint32_t)(walk >> 32), k0, k1);
+}
+
+__host__ __device__ __forceinline__ float uniform_from_word(uint32_t w) {
+  return (float)(w >> 8) * (1.0f / 16777216.0f);
+}
+
 }  // namespace walk_b200

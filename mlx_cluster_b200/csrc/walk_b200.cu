@@ -138,6 +138,14 @@ int launch_uniform_t(const UniformParams& P, cudaStream_t s) {
   int variant = g_tuning.uniform_variant.load();
   if (variant == 0) variant = P.walk_length >= 4 ? 7 : 1;
   const unsigned grid = (unsigned)blocks_for(P.num_walks);
+  if (P.generate) {  // draws generated in the kernel: the staged kernel only
+    if (USE_DESC && P.fused && g_tuning.uniform_fused.load() != 0) {
+      uniform_walk_staged_kernel<16, 4, true, HAS_EOUT, true, true><<<grid, kBlock, 0, s>>>(P);
+      return check_launch("uniform_walk_staged_kernel<16,4,fused,gen>");
+    }
+    uniform_walk_staged_kernel<16, 4, USE_DESC, HAS_EOUT, false, true><<<grid, kBlock, 0, s>>>(P);
+    return check_launch("uniform_walk_staged_kernel<16,4,gen>");
+  }
   if (USE_DESC && P.fused && variant != 1 && g_tuning.uniform_fused.load() != 0) {
     if (variant == 2) {
       uniform_walk_staged_kernel<8, 1, true, HAS_EOUT, true><<<grid, kBlock, 0, s>>>(P);
@@ -385,14 +393,57 @@ int walk_b200_shard_count_cyclic(int64_t num_walks, int32_t world_size, int32_t 
   return WALK_B200_OK;
 }
 
+namespace {
+int uniform_walk_impl(const walk_b200_csr* g, const int64_t* start, const float* rand, bool generate,
+                      uint64_t seed, uint64_t base, uint64_t stride, int64_t num_walks, int32_t walk_length,
+                      int64_t* n_out, int64_t* e_out, uint32_t* status_flags, void* stream);
+}
+
 int walk_b200_uniform_walk(const walk_b200_csr* g, const int64_t* start, const float* rand,
                            int64_t num_walks, int32_t walk_length, int64_t* n_out, int64_t* e_out,
                            uint32_t* status_flags, void* stream) {
+  return uniform_walk_impl(g, start, rand, false, 0, 0, 1, num_walks, walk_length, n_out, e_out, status_flags, stream);
+}
+
+int walk_b200_uniform_walk_philox(const walk_b200_csr* g, const int64_t* start, int64_t num_walks,
+                                  int32_t walk_length, uint64_t seed, uint64_t walk_index_base,
+                                  uint64_t walk_index_stride, int64_t* n_out, int64_t* e_out,
+                                  uint32_t* status_flags, void* stream) {
+  return uniform_walk_impl(g, start, nullptr, true, seed, walk_index_base, walk_index_stride ? walk_index_stride : 1,
+                           num_walks, walk_length, n_out, e_out, status_flags, stream);
+}
+
+void walk_b200_uniform_draw(uint64_t seed, uint64_t walk, uint32_t step, float* r) {
+  const Philox4 b = uniform_block((uint32_t)seed, (uint32_t)(seed >> 32), walk, step >> 2);
+  const uint32_t w = (step & 3) == 0 ? b.x : (step & 3) == 1 ? b.y : (step & 3) == 2 ? b.z : b.w;
+  if (r) *r = uniform_from_word(w);
+}
+
+void walk_b200_uniform_draws(uint64_t seed, uint64_t walk_index_base, uint64_t walk_index_stride,
+                             int64_t num_walks, int32_t walk_length, float* out) {
+  if (!out || num_walks <= 0 || walk_length <= 0) return;
+  if (walk_index_stride == 0) walk_index_stride = 1;
+  for (int64_t w = 0; w < num_walks; w++) {
+    const uint64_t gw = walk_index_base + (uint64_t)w * walk_index_stride;
+    for (int32_t l = 0; l < walk_length; l += 4) {
+      const Philox4 b = uniform_block((uint32_t)seed, (uint32_t)(seed >> 32), gw, (uint32_t)l >> 2);
+      const uint32_t words[4] = {b.x, b.y, b.z, b.w};
+      for (int k = 0; k < 4 && l + k < walk_length; k++) out[w * walk_length + l + k] = uniform_from_word(words[k]);
+    }
+  }
+}
+
+namespace {
+int uniform_walk_impl(const walk_b200_csr* g, const int64_t* start, const float* rand, bool generate,
+                      uint64_t seed, uint64_t base, uint64_t stride, int64_t num_walks, int32_t walk_length,
+                      int64_t* n_out, int64_t* e_out, uint32_t* status_flags, void* stream) {
   if (int rc = check_csr(g)) return rc;
   if (int rc = check_walk_sizes(num_walks, walk_length, start, n_out)) return rc;
-  if (num_walks > 0 && walk_length > 0 && !rand) return fail(WALK_B200_ERR_INVALID_ARG, "rand is NULL");
+  if (!generate && num_walks > 0 && walk_length > 0 && !rand) return fail(WALK_B200_ERR_INVALID_ARG, "rand is NULL");
   if (num_walks == 0) return WALK_B200_OK;
   UniformParams P{};
+  P.key0 = (uint32_t)seed; P.key1 = (uint32_t)(seed >> 32);
+  P.walk_index_base = base; P.walk_index_stride = stride;
   P.rowptr = g->rowptr; P.col = g->col; P.desc = g->rowdesc;
   P.num_nodes = g->num_nodes; P.num_edges = g->num_edges;
   P.start = start; P.rand = rand; P.num_walks = num_walks; P.walk_length = walk_length;
@@ -403,8 +454,10 @@ int walk_b200_uniform_walk(const walk_b200_csr* g, const int64_t* start, const f
       return fail(WALK_B200_ERR_INVALID_ARG, "fused edge records must be 16-byte aligned");
     P.fused = static_cast<const ulonglong2*>(g->fused);
   }
+  P.generate = generate ? 1 : 0;
   return launch_uniform(P, (cudaStream_t)stream);
 }
+}  // namespace
 
 int walk_b200_node2vec_walk(const walk_b200_csr* g, const int64_t* start, int64_t num_walks,
                             int32_t walk_length, double p, double q, uint64_t seed,
@@ -665,6 +718,7 @@ extern "C" int walk_b200_uniform_walk_noalloc(const int64_t* rowptr, const int64
     if (int rc = check_launch("rowdesc_pack_kernel")) return rc;
   }
   UniformParams P{};
+  P.walk_index_stride = 1;
   P.rowptr = rowptr; P.col = col; P.desc = num_nodes > 0 ? scratch : nullptr;
   P.num_nodes = num_nodes; P.num_edges = num_edges;
   P.start = start; P.rand = rand; P.num_walks = num_walks; P.walk_length = walk_length;

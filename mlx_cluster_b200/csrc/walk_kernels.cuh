@@ -225,6 +225,9 @@ struct UniformParams {
   int64_t* n_out;
   int64_t* e_out;
   uint32_t* flags;
+  int32_t generate;           // draws come from the kernel's own Philox stream instead of `rand`
+  uint32_t key0, key1;        // its key
+  uint64_t walk_index_base, walk_index_stride;
 };
 
 // One uniform step from `cur` with draw r. Same float32 arithmetic as the reference:
@@ -315,9 +318,12 @@ __global__ void __launch_bounds__(kBlock) uniform_walk_direct_kernel(const Unifo
 // segments of S consecutive int64. Global traffic on both sides is whole sectors; the
 // only divergent accesses left per step are the row fetch and the col gather. The next
 // chunk's rand is prefetched into registers while the current chunk walks.
-template <int S, int MIN_BLOCKS, bool USE_DESC, bool HAS_EOUT, bool FUSED = false>
+// GEN: no rand array; lane w draws step l from the Philox stream of its global walk index
+// (uniform_block / uniform_from_word), four steps per block, so nothing is read for the draws.
+template <int S, int MIN_BLOCKS, bool USE_DESC, bool HAS_EOUT, bool FUSED = false, bool GEN = false>
 __global__ void __launch_bounds__(kBlock, MIN_BLOCKS) uniform_walk_staged_kernel(const UniformParams P) {
   static_assert(!FUSED || USE_DESC, "fused edge records carry row descriptors");
+  static_assert(S % 4 == 0, "a Philox block serves four steps");
   constexpr int kPitch = 33;  // 8-byte slots per tile row: 32 lanes + 1 pad
   __shared__ unsigned long long tiles[kWarpsPerBlock][S][kPitch];
   const int lane = threadIdx.x & 31;
@@ -367,26 +373,37 @@ __global__ void __launch_bounds__(kBlock, MIN_BLOCKS) uniform_walk_staged_kernel
     }
   };
 
-  prefetch(0);
+  const uint64_t gw = P.walk_index_base + (uint64_t)w * P.walk_index_stride;
+  if (!GEN) prefetch(0);
   for (int64_t l0 = 0; l0 < L; l0 += S) {
     const int sc = (int)min((int64_t)S, L - l0);
     const int total = nw * sc;
+    if (!GEN) {
 #pragma unroll
-    for (int k = 0; k < S; k++) {
-      const int idx = k * 32 + lane;
-      if (idx < total) {
-        const int wi = (sc == S) ? idx / S : idx / sc;
-        const int j = idx - wi * sc;
-        tile[j][wi] = pre[k];
+      for (int k = 0; k < S; k++) {
+        const int idx = k * 32 + lane;
+        if (idx < total) {
+          const int wi = (sc == S) ? idx / S : idx / sc;
+          const int j = idx - wi * sc;
+          tile[j][wi] = pre[k];
+        }
       }
+      __syncwarp();
+      if (l0 + S < L) prefetch(l0 + S);
     }
-    __syncwarp();
-    if (l0 + S < L) prefetch(l0 + S);
     if (live) {
+      Philox4 blk = {0, 0, 0, 0};
       for (int j = 0; j < sc; j++) {
         int64_t e = -1;
         if (!parked) {
-          const float r = __uint_as_float((uint32_t)tile[j][lane]);
+          float r;
+          if (GEN) {
+            if ((j & 3) == 0) blk = uniform_block(P.key0, P.key1, gw, (uint32_t)((l0 + j) >> 2));
+            const uint32_t word = (j & 3) == 0 ? blk.x : (j & 3) == 1 ? blk.y : (j & 3) == 2 ? blk.z : blk.w;
+            r = uniform_from_word(word);
+          } else {
+            r = __uint_as_float((uint32_t)tile[j][lane]);
+          }
           e = FUSED ? uniform_step_fused(P, pol, cur, cur_rs, cur_deg, parked, r)
                     : uniform_step<USE_DESC>(P, pol, cur, parked, r);
         }

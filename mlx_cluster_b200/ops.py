@@ -285,7 +285,7 @@ def _finish(graph, out, e_out, check, return_edges):
 
 def random_walk(rowptr, col, start, rand, walk_length, *, stream=None, return_edges: bool = False,
                 check: bool = False, out: Optional[torch.Tensor] = None, graph: Optional[WalkGraph] = None,
-                fused: bool = False):
+                fused: bool = False, seed: int = 0, walk_index_base: int = 0, walk_index_stride: int = 1):
     """Uniform CSR random walk (``random_walk`` of the reference, ``bindings.cpp:12-21``).
 
     Step ``l`` of walk ``w`` moves from ``v`` to ``col[rowptr[v] + int(rand[w, l] * deg(v))]``
@@ -297,7 +297,10 @@ def random_walk(rowptr, col, start, rand, walk_length, *, stream=None, return_ed
     synchronises and raises if the kernel met malformed input; ``out`` supplies the output
     tensor; ``graph`` passes a prepared :class:`WalkGraph` instead of ``rowptr``/``col``;
     ``fused=True`` builds (once per graph, 16 bytes per edge) fused edge records that make a step
-    one gather instead of two -- worth it when many calls walk the same graph.
+    one gather instead of two -- worth it when many calls walk the same graph. ``rand=None``
+    (CUDA tensors only) lets the kernel generate the draws itself from a Philox stream keyed by
+    ``seed`` and indexed by the global walk (``walk_index_base + row * walk_index_stride``);
+    ``mlx_cluster_b200._lib.uniform_draws`` replays that stream on the host.
     """
     L = _check_walk_length(walk_length)
     if not isinstance(start, torch.Tensor) or not start.is_cuda:
@@ -306,10 +309,11 @@ def random_walk(rowptr, col, start, rand, walk_length, *, stream=None, return_ed
     g = graph if graph is not None else prepare_graph(_require(rowptr, "rowptr", torch.int64, dev),
                                                       _require(col, "col", torch.int64, dev), fused=fused)
     _require(start, "start", torch.int64, g.device)
-    _require(rand, "rand", torch.float32, g.device)
     n = start.numel()
-    if rand.numel() != n * L:
-        raise ValueError(f"rand must hold n * walk_length = {n * L} values, has {rand.numel()}")
+    if rand is not None:
+        _require(rand, "rand", torch.float32, g.device)
+        if rand.numel() != n * L:
+            raise ValueError(f"rand must hold n * walk_length = {n * L} values, has {rand.numel()}")
     with torch.cuda.device(dev):
         if out is None:
             out = torch.empty((n, L + 1), dtype=torch.int64, device=dev)
@@ -319,9 +323,14 @@ def random_walk(rowptr, col, start, rand, walk_length, *, stream=None, return_ed
                 raise ValueError("out has the wrong size")
         e_out = torch.empty((n, L), dtype=torch.int64, device=dev) if return_edges else None
         csr = g.csr()
-        _lib.check(_lib.lib().walk_b200_uniform_walk(
-            C.byref(csr), _ptr(start), _ptr(rand), n, L, _ptr(out), _ptr(e_out),
-            g.flags.data_ptr(), _stream_handle(stream, dev)))
+        if rand is None:
+            _lib.check(_lib.lib().walk_b200_uniform_walk_philox(
+                C.byref(csr), _ptr(start), n, L, int(seed) & (2**64 - 1), int(walk_index_base),
+                int(walk_index_stride), _ptr(out), _ptr(e_out), g.flags.data_ptr(), _stream_handle(stream, dev)))
+        else:
+            _lib.check(_lib.lib().walk_b200_uniform_walk(
+                C.byref(csr), _ptr(start), _ptr(rand), n, L, _ptr(out), _ptr(e_out),
+                g.flags.data_ptr(), _stream_handle(stream, dev)))
     return _finish(g, out, e_out, check, return_edges)
 
 

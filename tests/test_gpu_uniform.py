@@ -186,3 +186,34 @@ def test_every_step_follows_an_edge_at_full_length(cuda):
     for v in ("direct", "staged16"):
         _lib.set_tuning("uniform_variant", VARIANTS[v])
         assert torch.equal(out, random_walk(rowptr, col, start, rand, L))
+
+
+def test_draws_generated_in_the_kernel_match_their_host_replay(cuda):
+    """rand=None: the kernel draws from its own Philox stream; replaying that stream on the host
+    and feeding it to the reference loop must give the same walks, for any sharding of the rows."""
+    rng = np.random.default_rng(3)
+    for n_nodes, walks, L in [(300, 1000, 37), (50, 33, 3), (2000, 4097, 80), (64, 5, 0)]:
+        rowptr, col = random_csr(rng, n_nodes, 5.0, frac_isolated=0.1)
+        start = rng.integers(0, n_nodes, walks).astype(np.int64)
+        rand = _lib.uniform_draws(77, walks, L)
+        assert rand.shape == (walks, L) and (rand >= 0).all() and (rand < 1).all()
+        want_n, want_e = oracle.uniform_walk(rowptr, col, start, rand, L, return_edges=True)
+        for fused in (False, True):
+            g = WalkGraph(torch.from_numpy(rowptr).to(cuda), torch.from_numpy(col).to(cuda), fused=fused)
+            got_n, got_e = random_walk(None, None, torch.from_numpy(start).to(cuda), None, L, graph=g, seed=77,
+                                       return_edges=True, check=True)
+            np.testing.assert_array_equal(got_n.cpu().numpy(), want_n)
+            np.testing.assert_array_equal(got_e.cpu().numpy(), want_e)
+        for world in (2, 3):
+            for r in range(world):
+                part = random_walk(None, None, torch.from_numpy(start[r::world].copy()).to(cuda), None, L, graph=g,
+                                   seed=77, walk_index_base=r, walk_index_stride=world)
+                np.testing.assert_array_equal(part.cpu().numpy(), want_n[r::world])
+    # the host replay of single draws agrees with the bulk one
+    import ctypes as C
+    one = C.c_float(0)
+    bulk = _lib.uniform_draws(5, 3, 9, walk_index_base=10, walk_index_stride=4)
+    for w in range(3):
+        for l in range(9):
+            _lib.lib().walk_b200_uniform_draw(5, 10 + 4 * w, l, C.byref(one))
+            assert one.value == bulk[w, l]
