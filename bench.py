@@ -189,10 +189,15 @@ def cpu_walk_seconds(wl, rowptr, col, start, rand, procs):
     return time.perf_counter() - t, kind_impl, len(jobs)
 
 
+def start_order(n_nodes):
+    """The workload's start list: every node once, in the seeded random order the GPU arm uses."""
+    return torch.randperm(n_nodes, generator=torch.Generator().manual_seed(PHILOX_SEED)).numpy()
+
+
 def size_cpu_sample(wl, rowptr, col, n_total, target_s, procs, rng):
     """Pick how many of the workload's first start rows give about target_s of CPU work."""
     pilot = min(n_total, 2048 * procs)
-    start = np.arange(pilot, dtype=np.int64)
+    start = start_order(n_total)[:pilot]
     rand = rng.random((pilot, wl["L"]), dtype=np.float32) if wl["kind"] == "uniform" else None
     secs, _, _ = cpu_walk_seconds(wl, rowptr, col, start, rand, procs)
     rows = int(min(n_total, max(pilot, pilot * target_s / max(secs, 1e-6))))
@@ -213,7 +218,7 @@ def run_reference_arm(args, wl):
     budget_s = 150.0
     per_step = budget_s / max(1, args.steps + args.warmup)
     rows = size_cpu_sample(wl, rowptr, col, n_total, per_step, procs, rng)
-    start = np.arange(rows, dtype=np.int64)
+    start = start_order(n_total)[:rows]
     rand = rng.random((rows, L), dtype=np.float32) if wl["kind"] == "uniform" else None
     kind, used = "port", procs
     for _ in range(args.warmup):
@@ -240,7 +245,7 @@ def run_reference_arm(args, wl):
 def workload_config(wl, n_nodes, n_edges, gpus, membership=None, edge_records=None, rand_source=None):
     c = {"workload": args_workload_name(wl), "graph": f"R-MAT scale {wl['scale']} edge factor {wl['edge_factor']} "
          f"(a,b,c,d)=(0.57,0.19,0.19,0.05) seed {wl['seed']}, symmetrised, deduplicated, no self-loops, int64 CSR",
-         "num_nodes": n_nodes, "num_directed_edges": n_edges, "starts": "every node once", "walk_length": wl["L"],
+         "num_nodes": n_nodes, "num_directed_edges": n_edges, "starts": "every node once, in a seeded random order", "walk_length": wl["L"],
          "sharding": f"start rows dealt cyclically over {gpus} GPU(s), CSR replicated",
          "l2": "no flush between steps: col (8 B x edges) is far larger than the 126 MB L2"}
     if wl["kind"] == "node2vec":
@@ -317,10 +322,15 @@ def run_ours(args, wl):
     _lib.lib()  # fail now if the CUDA library is missing
     rowptr, col, build_s = build_graph(wl, dev, world, rank)
     n_nodes, n_edges, L = rowptr.numel() - 1, col.numel(), wl["L"]
-    # cyclic shards (rank r walks start rows r, r + G, ...): block shards of an R-MAT graph differ by
-    # a quarter in work because node id and degree are correlated
+    # Every node starts one walk; the start list is a seeded random order of the nodes and is dealt
+    # cyclically (rank r walks rows r, r + G, ...). On R-MAT every bit of a node id is correlated with
+    # its degree, so shards cut by id -- blocks or strides of the natural order -- differ by up to 3x
+    # in work; a random order makes any split even. Draws are indexed by the row, so the walks do
+    # not depend on the GPU count.
     row_slice, (b, stride) = shard_rows(n_nodes, world, rank, "cyclic")
-    start = torch.arange(n_nodes, dtype=torch.int64, device=dev)[row_slice].contiguous()
+    order = torch.randperm(n_nodes, generator=torch.Generator().manual_seed(PHILOX_SEED))
+    start = order[row_slice].contiguous().to(dev)
+    del order
     rows = start.numel()
     t_prep = time.perf_counter()
     graph = WalkGraph(rowptr, col, symmetric=True, edgeset=(wl["kind"] == "node2vec" and args.membership == "hash"),
@@ -394,9 +404,9 @@ def run_ours(args, wl):
     if rank == 0 and not args.no_probe:
         ceiling = _lib.gather_probe(2 << 30, 32)
         if wl["kind"] == "node2vec":
-            # every row fetch, candidate gather and hash bucket is one random access (upper bound on DRAM misses)
-            accesses = cnt["steps_first"] + cnt["steps_deg1"] + cnt["steps_sampled"] + rows \
-                + cnt["attempts"] + cnt["steps_first"] + cnt["steps_deg1"] + cnt["probes"]
+            # every gather the kernel issued is one random access; a hash bucket (counted as four 8-byte
+            # loads) is one access too (upper bound on DRAM misses)
+            accesses = cnt["loads"] - (3 * cnt["probes"] if args.membership == "hash" else 0)
         else:
             accesses = (moved + 2 * rows) if not args.no_fused else (2 * moved + rows)
         roofline["random_access"] = {"ceiling_gathers_per_s": ceiling, "gathers_per_launch": int(accesses),
@@ -449,7 +459,7 @@ def run_ours(args, wl):
         rp, cl = rowptr.cpu().numpy(), col.cpu().numpy()
         rng = np.random.default_rng(0)
         n_rows = size_cpu_sample(wl, rp, cl, n_nodes, args.cpu_seconds, 1, rng)
-        s = np.arange(n_rows, dtype=np.int64)
+        s = start_order(n_nodes)[:n_rows]
         r = rng.random((n_rows, L), dtype=np.float32) if wl["kind"] == "uniform" else None
         secs, kind, used = cpu_walk_seconds(wl, rp, cl, s, r, 1)
         cpu = {"value": n_rows * L / secs, "unit": "steps/s", "cores": used, "kind": kind,
