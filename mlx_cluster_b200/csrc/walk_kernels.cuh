@@ -537,6 +537,7 @@ struct Node2vecParams {
   uint64_t walk_index_base;
   uint64_t walk_index_stride;
   uint32_t max_attempts;
+  int32_t batch_lanes, batch_trips;  // batching of the rare state paths (see the kernel)
   int64_t* n_out;
   int64_t* e_out;
   uint32_t* flags;
@@ -544,16 +545,24 @@ struct Node2vecParams {
   unsigned long long* queue;  // launch-wide chunk counter, zero at launch
 };
 
-enum : int { ST_IDLE = 0, ST_START, ST_ROW, ST_ATTEMPT, ST_XROW, ST_SEARCH, ST_HASH };
+enum : int { ST_IDLE = 0, ST_START, ST_ROW, ST_ACCEPTED, ST_ATTEMPT, ST_XROW, ST_SEARCH, ST_HASH };
 enum : int { MEMBER_SEARCH_PREV = 0, MEMBER_SEARCH_CAND = 1, MEMBER_HASH = 2 };
 
 // Persistent warps; one walk per lane; one gather per loop trip whatever the lane is doing.
-//   ST_START    fetch the start node of a freshly assigned walk
-//   ST_ROW      fetch the bounds of the current node's row
-//   ST_ATTEMPT  draw a candidate edge (Philox) and gather col[e]
-//   ST_XROW     (MEMBER_SEARCH_CAND) fetch the bounds of the candidate's row
-//   ST_SEARCH   one binary-search probe of the membership test
-//   ST_HASH     (MEMBER_HASH) one 32-byte bucket of the edge hash set
+//   ST_START     fetch the start node of a freshly assigned walk
+//   ST_ROW       fetch the bounds of the current node's row (REV: and the reverse position)
+//   ST_ACCEPTED  a step was decided: write it, advance, then continue as ST_ROW in the same trip
+//   ST_ATTEMPT   draw a candidate edge (Philox), classify it, gather col[e] if needed
+//   ST_XROW      (MEMBER_SEARCH_CAND) fetch the bounds of the candidate's row
+//   ST_SEARCH    one binary-search probe of the membership test
+//   ST_HASH      (MEMBER_HASH) one 32-byte bucket of the edge hash set
+// A warp executes the union of the paths its lanes are on, so a path that only one or two
+// lanes need costs as many issue slots as one all 32 need. The draw path (ST_ATTEMPT) is by far
+// the most frequent; the others are rare per lane but almost always present somewhere in the
+// warp. They are therefore batched: lanes that reach ST_HASH, or ST_ACCEPTED/ST_ROW/ST_START,
+// wait in that state until batch_lanes lanes of the warp are there (or batch_trips trips have
+// passed, or no lane has heavy work), and then the path runs once for all of them. Most trips
+// execute the draw path alone.
 // A lane whose walk ends takes the next unassigned walk of its warp's current chunk of
 // 32; a warp whose chunk is used up takes the next chunk from a launch-wide counter
 // (one atomicAdd per 32 walks). Walk cost varies by orders of magnitude (isolated start:
@@ -588,6 +597,7 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
   const int64_t n_chunks = (n + 31) / 32;
   int64_t q_next = 0, q_end = 0;  // empty: the first trip fetches a chunk
   bool drained = false;           // the launch-wide counter has run past the last chunk
+  int wait_hash = 0, wait_row = 0;  // trips the batched paths have been held back
 
   uint32_t c_loads = 0, c_attempts = 0, c_member = 0, c_probes = 0, c_formula = 0;
   uint32_t c_deg0 = 0, c_deg1 = 0, c_sampled = 0, c_first = 0;
@@ -633,15 +643,40 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
       }
     }
 
-    if (state != ST_IDLE) {
-      int64_t* out = P.n_out + i * ((int64_t)L + 1);
-      int64_t* eout = HAS_EOUT ? P.e_out + i * (int64_t)L : nullptr;
+    // ---- which batched paths run this trip (warp-uniform decisions)
+    const bool heavy = state == ST_ATTEMPT || state == ST_SEARCH || state == ST_XROW;
+    const bool in_hash = state == ST_HASH;
+    const bool in_row = state == ST_ROW || state == ST_ACCEPTED || state == ST_START;
+    const unsigned m_heavy = __ballot_sync(kFull, heavy);
+    const unsigned m_hash = __ballot_sync(kFull, in_hash);
+    const unsigned m_row = __ballot_sync(kFull, in_row);
+    bool go_hash = false, go_row = false;
+    if (m_hash) {
+      go_hash = __popc(m_hash) >= P.batch_lanes || !m_heavy || ++wait_hash >= P.batch_trips;
+      if (go_hash) wait_hash = 0;
+    }
+    if (m_row) {
+      go_row = __popc(m_row) >= P.batch_lanes || !m_heavy || ++wait_row >= P.batch_trips;
+      if (go_row) wait_row = 0;
+    }
 
+    if (heavy || (in_hash && go_hash) || (in_row && go_row)) {
       bool accept = false, reject = false;
       bool need_load = true;  // REV: some attempts are decided without touching memory
 
+      if (state == ST_ACCEPTED) {  // write the decided step, advance, go on to the next row fetch
+        int64_t* out = P.n_out + i * ((int64_t)L + 1);
+        st8(out + l + 1, (int64_t)x, pol.stream);
+        if (HAS_EOUT) P.e_out[i * (int64_t)L + l] = (a >= P.max_attempts) ? -1 : (int64_t)e;
+        t = v; t_rs = v_rs; t_re = v_re;
+        v = x;
+        l++;
+        if (l == L) { state = ST_IDLE; need_load = false; }
+        else state = ST_ROW;
+      }
+
       // ---- address of this trip's gather
-      const void* addr;
+      const void* addr = nullptr;
       uint64_t policy = pol.stream;
       if (state == ST_START) {
         addr = P.start + i;
@@ -686,7 +721,7 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
       } else if (state == ST_SEARCH) {
         addr = col + (int64_t)(lo + (hi - lo) / 2);
         policy = pol.normal;  // upper levels of a hub row's search tree are shared by many walks
-      } else {  // ST_HASH
+      } else if (state == ST_HASH) {
         addr = P.edgeset + (uint64_t)lo * kEdgeSlotsPerBucket;
       }
 
@@ -716,13 +751,14 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
       if (!need_load) {
         // nothing was loaded
       } else if (state == ST_START) {
+        int64_t* out = P.n_out + i * ((int64_t)L + 1);
         out[0] = val;
         t = (idx_t)val;
         v = (idx_t)val;
         l = 0;
         if ((uint64_t)val >= (uint64_t)P.num_nodes) {
           raise_flag(P.flags, WALK_B200_FLAG_BAD_NODE);
-          for (int32_t k = 0; k < L; k++) { out[k + 1] = val; if (HAS_EOUT) eout[k] = -1; }
+          for (int32_t k = 0; k < L; k++) { out[k + 1] = val; if (HAS_EOUT) P.e_out[i * (int64_t)L + k] = -1; }
           state = ST_IDLE;
         } else {
           state = L > 0 ? ST_ROW : ST_IDLE;
@@ -736,7 +772,8 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
           if (deg == 0) {
             // stay in place for every remaining step
             if (COUNT) c_deg0 += (uint32_t)(L - l);
-            for (int32_t k = l; k < L; k++) { st8(out + k + 1, (int64_t)v, pol.stream); if (HAS_EOUT) eout[k] = -1; }
+            int64_t* out = P.n_out + i * ((int64_t)L + 1);
+            for (int32_t k = l; k < L; k++) { st8(out + k + 1, (int64_t)v, pol.stream); if (HAS_EOUT) P.e_out[i * (int64_t)L + k] = -1; }
             state = ST_IDLE;
           } else {
             v_rs = (idx_t)rs;
@@ -801,7 +838,7 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
           if (val < key) lo = mid + 1; else hi = mid;
           if (!(lo < hi)) reject = true;     // not a member, and the draw is known to be >= cut2
         }
-      } else {  // ST_HASH
+      } else if (state == ST_HASH) {
         if (COUNT) c_probes++;
         const uint64_t key = edge_key((uint64_t)x, (uint64_t)t);
         if (h0.x == key || h0.y == key || h1.x == key || h1.y == key) accept = true;
@@ -821,14 +858,7 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
           if (REV) e = (idx_t)kUnknownEdge;
         }
       }
-      if (accept) {
-        st8(out + l + 1, (int64_t)x, pol.stream);
-        if (HAS_EOUT) eout[l] = (a >= P.max_attempts) ? -1 : (int64_t)e;
-        t = v; t_rs = v_rs; t_re = v_re;
-        v = x;
-        l++;
-        state = (l == L) ? ST_IDLE : ST_ROW;
-      }
+      if (accept) state = ST_ACCEPTED;  // written and advanced when the row path next runs
     }
   }
 
