@@ -607,6 +607,7 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
   idx_t v_rs = 0, v_re = 0;       // row [start, end) of v
   idx_t t_rs = 0, t_re = 0;       // row [start, end) of t (MEMBER_SEARCH_PREV range)
   uint32_t v_deg = 0;             // degree of v saturated at 2^31 (enough for "u % deg" with 31-bit u)
+  uint32_t v_inv = 0;             // floor((2^32 - 1) / v_deg): "u % v_deg" as a multiply and one fix-up
   using uidx_t = typename std::conditional<sizeof(idx_t) == 4, uint32_t, uint64_t>::type;
   uidx_t lo = 0, hi = 0;          // search window / hash bucket + probe count / parked accept draw
   idx_t e = 0;                    // sampled edge index
@@ -689,7 +690,10 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
         } else {
           uint32_t cand, acc;
           node2vec_draw(P.key0, P.key1, P.walk_index_base + (uint64_t)i * P.walk_index_stride, (uint32_t)l, a, cand, acc);
-          e = v_rs + (idx_t)(cand % v_deg);
+          // cand % v_deg, exactly: the quotient estimate is at most one too small for a 31-bit cand
+          uint32_t rem = cand - __umulhi(cand, v_inv) * v_deg;
+          if (rem >= v_deg) rem -= v_deg;
+          e = v_rs + (idx_t)rem;
           lo = acc;  // parked until the candidate arrives
         }
         addr = col + (int64_t)e;
@@ -779,6 +783,7 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
             v_rs = (idx_t)rs;
             v_re = (idx_t)(rs + deg);
             v_deg = deg > 0x7fffffffll ? 0x80000000u : (uint32_t)deg;
+            v_inv = 0xffffffffu / v_deg;
             a = 0;
             if (REV) ret_e = (idx_t)rev;
             state = ST_ATTEMPT;
