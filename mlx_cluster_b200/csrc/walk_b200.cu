@@ -58,6 +58,8 @@ struct Tuning {
   std::atomic<int32_t> n2v_member{0};       // 0 auto (hash set when the graph has one), 1 ignore the hash set
   std::atomic<int32_t> n2v_batch_lanes{4};  // rare state paths wait for this many lanes of a warp ...
   std::atomic<int32_t> n2v_batch_trips{4};  // ... or this many trips (measured best: 4/4)
+  std::atomic<int32_t> n2v_draw_loop{3};    // memory-free rejections consumed per trip (reverse-position kernel;
+                                            // measured: 1 -> 193 ms, 2 -> 169, 3 -> 166, 4 -> 170, 8 -> 207)
   std::atomic<int32_t> n2v_rev{1};          // 1 auto (reverse positions when they pay), 0 never, 2 whenever available
   std::atomic<int32_t> n2v_blocks_per_sm{0};  // 0 = what the occupancy calculator allows
   std::atomic<int32_t> l2_hints{3};         // bit 0: evict-last row bounds, bit 1: evict-first streams
@@ -75,6 +77,7 @@ std::atomic<int32_t>* tuning_slot(const char* key) {
   if (!strcmp(key, "n2v_rev")) return &g_tuning.n2v_rev;
   if (!strcmp(key, "n2v_batch_lanes")) return &g_tuning.n2v_batch_lanes;
   if (!strcmp(key, "n2v_batch_trips")) return &g_tuning.n2v_batch_trips;
+  if (!strcmp(key, "n2v_draw_loop")) return &g_tuning.n2v_draw_loop;
   if (!strcmp(key, "n2v_blocks_per_sm")) return &g_tuning.n2v_blocks_per_sm;
   if (!strcmp(key, "l2_hints")) return &g_tuning.l2_hints;
   if (!strcmp(key, "l2_fetch_granularity")) return &g_tuning.l2_fetch_granularity;
@@ -486,6 +489,8 @@ int walk_b200_node2vec_walk(const walk_b200_csr* g, const int64_t* start, int64_
   P.batch_trips = g_tuning.n2v_batch_trips.load();
   if (P.batch_lanes < 1) P.batch_lanes = 1;
   if (P.batch_trips < 1) P.batch_trips = 1;
+  P.draw_loop = g_tuning.n2v_draw_loop.load();
+  if (P.draw_loop < 1) P.draw_loop = 1;
   P.n_out = n_out; P.e_out = walk_length > 0 ? e_out : nullptr;
   P.flags = status_flags; P.counters = (unsigned long long*)counters;
   P.hints = g_tuning.l2_hints.load();

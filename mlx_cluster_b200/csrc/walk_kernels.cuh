@@ -538,6 +538,7 @@ struct Node2vecParams {
   uint64_t walk_index_stride;
   uint32_t max_attempts;
   int32_t batch_lanes, batch_trips;  // batching of the rare state paths (see the kernel)
+  int32_t draw_loop;                 // REV: memory-free rejections consumed per trip
   int64_t* n_out;
   int64_t* e_out;
   uint32_t* flags;
@@ -688,12 +689,23 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
         if (v_deg == 1) {
           e = v_rs;  // forced move: no draw (deg-1 shortcut of the reference; also exact at step 0)
         } else {
+          // REV: attempts that are rejected without touching memory (not the way back, accept draw
+          // above cut1 and cut2) are consumed right here, up to draw_loop of them per trip, instead
+          // of costing a whole trip of the state machine each.
+          const uint64_t gw = P.walk_index_base + (uint64_t)i * P.walk_index_stride;
+          const bool may_skip = REV && l > 0 && ret_e != (idx_t)kUnknownEdge;
           uint32_t cand, acc;
-          node2vec_draw(P.key0, P.key1, P.walk_index_base + (uint64_t)i * P.walk_index_stride, (uint32_t)l, a, cand, acc);
-          // cand % v_deg, exactly: the quotient estimate is at most one too small for a 31-bit cand
-          uint32_t rem = cand - __umulhi(cand, v_inv) * v_deg;
-          if (rem >= v_deg) rem -= v_deg;
-          e = v_rs + (idx_t)rem;
+          for (int k = 1;; k++) {
+            node2vec_draw(P.key0, P.key1, gw, (uint32_t)l, a, cand, acc);
+            // cand % v_deg, exactly: the quotient estimate is at most one too small for a 31-bit cand
+            uint32_t rem = cand - __umulhi(cand, v_inv) * v_deg;
+            if (rem >= v_deg) rem -= v_deg;
+            e = v_rs + (idx_t)rem;
+            if (!may_skip || e == ret_e || acc < P.cut2 || acc < P.cut1) break;
+            if (k >= P.draw_loop || a + 1 >= P.max_attempts) break;  // leave it to the regular path below
+            if (COUNT) c_attempts++;
+            a++;
+          }
           lo = acc;  // parked until the candidate arrives
         }
         addr = col + (int64_t)e;
