@@ -34,7 +34,7 @@ extern "C" {
 /* ---- return codes ---- */
 #define WALK_B200_OK 0
 #define WALK_B200_ERR_INVALID_ARG 1 /* null pointer, negative size, size overflow */
-#define WALK_B200_ERR_BAD_PQ 2      /* p or q not finite, not > 0, or acceptance threshold below 2^-16 */
+#define WALK_B200_ERR_BAD_PQ 2      /* p or q not finite, not > 0, or prob_2 = (1/q)/max(1/p, 1, 1/q) below 2^-16 */
 #define WALK_B200_ERR_CUDA 3        /* a CUDA runtime call failed (message has the CUDA error) */
 #define WALK_B200_ERR_CSR_INVALID 4 /* walk_b200_csr_validate / host entry points found a malformed graph */
 #define WALK_B200_ERR_UNSUPPORTED 5 /* e.g. row descriptor cannot represent this graph */

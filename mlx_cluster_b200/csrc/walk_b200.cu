@@ -51,8 +51,8 @@ int check_launch(const char* what) {
 
 // ---- tuning knobs (experiments; defaults are the measured best) ------------------
 struct Tuning {
-  std::atomic<int32_t> uniform_variant{0};  // 0 auto, 1 direct, 2 staged S=8, 3 staged S=16, 4 staged S=4,
-                                            // 5 staged S=16 capped at 40 registers, 6 staged S=8 capped at 32
+  std::atomic<int32_t> uniform_variant{0};  // 0 auto (7; 1 for walk_length < 4), 1 direct, staged: 2 S=8, 3 S=16,
+                                            // 4 S=4, 5 S=16 @6 blocks/SM, 6 S=8 @8, 7 S=16 @4, 8 S=16 @5, 9 S=8 @6
   std::atomic<int32_t> uniform_fused{1};    // use fused edge records when the graph has them
   std::atomic<int32_t> n2v_idx{0};          // 0 auto (32-bit indices when they fit), 1 force 64-bit
   std::atomic<int32_t> n2v_member{0};       // 0 auto (hash set when the graph has one), 1 ignore the hash set
@@ -129,13 +129,13 @@ int thresholds(double p, double q, double prob[3], uint32_t cuts[3]) {
   prob[0] = 1. / p / max_prob;
   prob[1] = 1. / max_prob;
   prob[2] = 1. / q / max_prob;
-  for (int k = 0; k < 3; k++) {
-    if (!(prob[k] >= 1.0 / 65536.0))
-      return fail(WALK_B200_ERR_BAD_PQ,
-                  "p=%g, q=%g give an acceptance threshold of %g (< 2^-16): the rejection loop would not end",
-                  p, q, prob[k]);
-    cuts[k] = accept_cut(prob[k]);
-  }
+  // prob_2 applies to every candidate, so it bounds the expected attempts of a step by 1 / prob_2
+  // whatever the graph looks like; below 2^-16 a step can take longer than anyone will wait
+  if (!(prob[2] >= 1.0 / 65536.0))
+    return fail(WALK_B200_ERR_BAD_PQ,
+                "p=%g, q=%g give prob_2 = %g (< 2^-16): the rejection loop would need more than 65536 attempts per step",
+                p, q, prob[2]);
+  for (int k = 0; k < 3; k++) cuts[k] = accept_cut(prob[k]);
   return WALK_B200_OK;
 }
 

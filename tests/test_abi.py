@@ -68,6 +68,14 @@ def test_bad_pq_is_rejected(walklib, p, q):
     assert walklib.walk_b200_last_error()
 
 
+def test_extreme_but_workable_pq_is_accepted(walklib):
+    # a huge p only makes returning unlikely; every candidate is still accepted with prob_2 = 1
+    prob, cuts = _lib.node2vec_thresholds(1e6, 1.0)
+    assert prob[2] == 1.0 and prob[0] == 1e-6 and cuts[0] == oracle.accept_cut(1e-6)
+    prob, _ = _lib.node2vec_thresholds(1.0, 60000.0)
+    assert prob[2] >= 2.0 ** -16
+
+
 def test_shard_range_partitions(walklib):
     for n in [0, 1, 7, 8, 9, 1000, 2708, 16777216]:
         for world in [1, 2, 3, 4, 8]:
