@@ -35,6 +35,11 @@ WORKLOADS = {
     "node2vec_rmat20": dict(kind="node2vec", scale=20, edge_factor=16, seed=2, L=80, p=0.25, q=4.0),
     "uniform_rmat20": dict(kind="uniform", scale=20, edge_factor=16, seed=1, L=80),
     "node2vec_rmat22_p1q2": dict(kind="node2vec", scale=22, edge_factor=16, seed=3, L=40, p=1.0, q=2.0),
+    # the largest configuration: 2^26 nodes, ~2e9 directed edges, 10 walks per node, for 8 GPUs
+    # (or one rank's share of it on one GPU with --shard-of 8)
+    "uniform_rmat26": dict(kind="uniform", scale=26, edge_factor=16, seed=3, L=40, walks_per_node=10),
+    "node2vec_rmat26_p1q2": dict(kind="node2vec", scale=26, edge_factor=16, seed=3, L=40, p=1.0, q=2.0,
+                                 walks_per_node=10),
 }
 RMAT = dict(a=0.57, b=0.19, c=0.19, d=0.05)
 # DRAM bytes (read + write) per launch of the dominant kernel, from the ncu captures summarised under
@@ -189,15 +194,24 @@ def cpu_walk_seconds(wl, rowptr, col, start, rand, procs):
     return time.perf_counter() - t, kind_impl, len(jobs)
 
 
-def start_order(n_nodes):
-    """The workload's start list: every node once, in the seeded random order the GPU arm uses."""
-    return torch.randperm(n_nodes, generator=torch.Generator().manual_seed(PHILOX_SEED)).numpy()
+def start_order(n_nodes, walks_per_node=1, device=None):
+    """The workload's start list: every node `walks_per_node` times, in a seeded random order (a
+    tensor on `device`). Lists of up to 2^26 rows are drawn with the CPU generator, larger ones on
+    the device (same result on every rank of one machine type)."""
+    total = n_nodes * walks_per_node
+    if total <= (1 << 26) or device is None or torch.device(device).type != "cuda":
+        order = torch.randperm(total, generator=torch.Generator().manual_seed(PHILOX_SEED))
+        if device is not None:
+            order = order.to(device)
+    else:
+        order = torch.randperm(total, generator=torch.Generator(device=device).manual_seed(PHILOX_SEED), device=device)
+    return order % n_nodes if walks_per_node > 1 else order
 
 
 def size_cpu_sample(wl, rowptr, col, n_total, target_s, procs, rng):
     """Pick how many of the workload's first start rows give about target_s of CPU work."""
     pilot = min(n_total, 2048 * procs)
-    start = start_order(n_total)[:pilot]
+    start = start_order(n_total, wl.get("walks_per_node", 1))[:pilot].numpy()
     rand = rng.random((pilot, wl["L"]), dtype=np.float32) if wl["kind"] == "uniform" else None
     secs, _, _ = cpu_walk_seconds(wl, rowptr, col, start, rand, procs)
     rows = int(min(n_total, max(pilot, pilot * target_s / max(secs, 1e-6))))
@@ -218,7 +232,7 @@ def run_reference_arm(args, wl):
     budget_s = 150.0
     per_step = budget_s / max(1, args.steps + args.warmup)
     rows = size_cpu_sample(wl, rowptr, col, n_total, per_step, procs, rng)
-    start = start_order(n_total)[:rows]
+    start = start_order(n_total, wl.get("walks_per_node", 1))[:rows].numpy()
     rand = rng.random((rows, L), dtype=np.float32) if wl["kind"] == "uniform" else None
     kind, used = "port", procs
     for _ in range(args.warmup):
@@ -245,7 +259,7 @@ def run_reference_arm(args, wl):
 def workload_config(wl, n_nodes, n_edges, gpus, membership=None, edge_records=None, rand_source=None):
     c = {"workload": args_workload_name(wl), "graph": f"R-MAT scale {wl['scale']} edge factor {wl['edge_factor']} "
          f"(a,b,c,d)=(0.57,0.19,0.19,0.05) seed {wl['seed']}, symmetrised, deduplicated, no self-loops, int64 CSR",
-         "num_nodes": n_nodes, "num_directed_edges": n_edges, "starts": "every node once, in a seeded random order", "walk_length": wl["L"],
+         "num_nodes": n_nodes, "num_directed_edges": n_edges, "starts": f"every node {wl.get('walks_per_node', 1)}x, in a seeded random order", "walk_length": wl["L"],
          "sharding": f"start rows dealt cyclically over {gpus} GPU(s), CSR replicated",
          "l2": "no flush between steps: col (8 B x edges) is far larger than the 126 MB L2"}
     if wl["kind"] == "node2vec":
@@ -330,11 +344,16 @@ def run_ours(args, wl):
     # its degree, so shards cut by id -- blocks or strides of the natural order -- differ by up to 3x
     # in work; a random order makes any split even. Draws are indexed by the row, so the walks do
     # not depend on the GPU count.
-    row_slice, (b, stride) = shard_rows(n_nodes, world, rank, "cyclic")
-    order = torch.randperm(n_nodes, generator=torch.Generator().manual_seed(PHILOX_SEED))
+    wpn = wl.get("walks_per_node", 1)
+    n_walks = n_nodes * wpn
+    shard_world, shard_rank = (args.shard_of, 0) if (world == 1 and args.shard_of > 1) else (world, rank)
+    row_slice, (b, stride) = shard_rows(n_walks, shard_world, shard_rank, "cyclic")
+    order = start_order(n_nodes, wpn, dev)
     start = order[row_slice].contiguous().to(dev)
     del order
+    torch.cuda.empty_cache()
     rows = start.numel()
+    walks_timed = n_walks if shard_world == world else rows  # a lone rank's share counts only its own rows
     t_prep = time.perf_counter()
     graph = WalkGraph(rowptr, col, symmetric=True, edgeset=(wl["kind"] == "node2vec" and args.membership == "hash"),
                       fused=(wl["kind"] == "uniform" and not args.no_fused))
@@ -368,7 +387,9 @@ def run_ours(args, wl):
         deg = rowptr.diff()
         cnt = {}
         random_walk(None, None, start, rand, L, graph=graph, out=out, check=True)
-        moved = int((deg[out[:, :-1].reshape(-1)] > 0).sum().item())
+        moved = 0
+        for c0 in range(0, rows, 1 << 22):  # in slices: the index tensor of the whole matrix would not fit beside it
+            moved += int((deg[out[c0:c0 + (1 << 22), :-1].reshape(-1)] > 0).sum().item())
         stay = rows * L - moved
         # per step: row bounds 16 (8 via the packed descriptor, counted as the CSR's 16) + rand 4 + col 8 + out 8
         alg_bytes = rows * 16 + moved * 36 + stay * 24
@@ -390,7 +411,7 @@ def run_ours(args, wl):
     clocks = sampler.stop() if sampler else None
     ms_per_step = allmax(total_ms / args.steps)
     kernel_ms = statistics.mean(per)
-    value = n_nodes * L / (ms_per_step * 1e-3)
+    value = walks_timed * L / (ms_per_step * 1e-3)
     peak, peak_kind = measured_peak_gbs()
     achieved = allsum(alg_bytes / (kernel_ms * 1e-3) / 1e9) / world  # mean per-GPU GB/s
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -449,7 +470,7 @@ def run_ours(args, wl):
             host_step()
         dt = time.perf_counter() - t0
         e2e_ms = allmax(1e3 * dt / e2e_steps)
-        e2e = {"value": n_nodes * L / (e2e_ms * 1e-3), "unit": "steps/s",
+        e2e = {"value": walks_timed * L / (e2e_ms * 1e-3), "unit": "steps/s",
                "h2d_bytes_per_step": int(allsum(rows * 8 + (rows * L * 4 if rand is not None else 0))),
                "d2h_bytes_per_step": int(allsum(rows * (L + 1) * 8)), "ms_per_step": e2e_ms, "steps": e2e_steps,
                "api": "walk_b200_*_walk_host (C ABI, pinned host buffers, graph resident)",
@@ -462,7 +483,7 @@ def run_ours(args, wl):
         rp, cl = rowptr.cpu().numpy(), col.cpu().numpy()
         rng = np.random.default_rng(0)
         n_rows = size_cpu_sample(wl, rp, cl, n_nodes, args.cpu_seconds, 1, rng)
-        s = start_order(n_nodes)[:n_rows]
+        s = start_order(n_nodes, wpn)[:n_rows].numpy()
         r = rng.random((n_rows, L), dtype=np.float32) if wl["kind"] == "uniform" else None
         secs, kind, used = cpu_walk_seconds(wl, rp, cl, s, r, 1)
         cpu = {"value": n_rows * L / secs, "unit": "steps/s", "cores": used, "kind": kind,
@@ -474,7 +495,7 @@ def run_ours(args, wl):
             "metric": "walk_steps_per_sec", "value": value, "unit": "steps/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int64", "data": "synthetic",
-            "config": workload_config(wl, n_nodes, n_edges, world, args.membership,
+            "config": workload_config(wl, n_nodes, n_edges, shard_world, args.membership,
                                       "col + row descriptors" if args.no_fused else "fused 16-byte records",
                                       "generated in the kernel (Philox4x32-10)" if args.device_rand else None),
             "roofline": roofline, "cpu_baseline": cpu,
@@ -499,6 +520,9 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="target CPU time of the cpu_baseline sample")
     ap.add_argument("--membership", default="hash", choices=["hash", "search"],
                     help="node2vec membership test: edge hash set (built once per graph) or binary search over col")
+    ap.add_argument("--shard-of", type=int, default=1,
+                    help="single process only: walk rank 0's share of this many ranks (sizes the largest workload "
+                         "for one GPU); value then counts this share alone")
     ap.add_argument("--device-rand", action="store_true",
                     help="uniform walk: generate the draws in the kernel instead of reading a rand array")
     ap.add_argument("--no-fused", action="store_true", help="uniform walk: do not build fused edge records")
