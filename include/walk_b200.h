@@ -290,6 +290,16 @@ int walk_b200_uniform_walk_noalloc(const int64_t* rowptr, const int64_t* col, in
                                    int64_t* e_out, uint32_t* status_flags, void* stream);
 
 /*
+ * Consumer of the walk matrix, the step that follows the walks in a node2vec pipeline (no counterpart
+ * in the reference, whose README lists further algorithms as future work, README.md:65-69): all runs of
+ * context_size consecutive nodes of every walk, windows[(w * nwin + j) * cs + k] = walks[w, j + k] with
+ * nwin = walk_length + 2 - context_size; column 0 is the centre node, the rest its skip-gram context.
+ * windows is int64 [num_walks * nwin, context_size], device, caller-allocated.
+ */
+int walk_b200_context_windows(const int64_t* walks, int64_t num_walks, int32_t walk_length,
+                              int32_t context_size, int64_t* windows, void* stream);
+
+/*
  * Device probe (diagnostic; allocates and frees array_bytes of device memory itself):
  * the rate of dependent random 8-byte gathers over an array much larger than L2, one
  * gather in flight per thread -- the access pattern of a walk step. On B200 this rate,

@@ -30,7 +30,7 @@ EXPORTS = (
     "walk_b200_graph_device_bytes", "walk_b200_uniform_walk_host", "walk_b200_node2vec_walk_host",
     "walk_b200_l2_window_set", "walk_b200_l2_window_clear",
     "walk_b200_set_tuning", "walk_b200_get_tuning",
-    "walk_b200_uniform_walk_noalloc", "walk_b200_gather_probe",
+    "walk_b200_uniform_walk_noalloc", "walk_b200_gather_probe", "walk_b200_context_windows",
 )
 NOALLOC_MAX_NODES = 1 << 20
 
@@ -93,6 +93,7 @@ def lib():
     L.walk_b200_l2_window_set.argtypes = [vp, C.c_size_t, C.c_float, vp, C.POINTER(C.c_size_t)]
     L.walk_b200_l2_window_clear.argtypes = [vp]
     L.walk_b200_uniform_walk_noalloc.argtypes = [vp, vp, i64, i64, vp, vp, i64, i32, vp, vp, vp, vp]
+    L.walk_b200_context_windows.argtypes = [vp, i64, i32, i32, vp, vp]
     L.walk_b200_gather_probe.argtypes = [C.c_size_t, i32, C.POINTER(dbl)]
     L.walk_b200_set_tuning.argtypes = [C.c_char_p, i32]
     L.walk_b200_get_tuning.argtypes = [C.c_char_p, C.POINTER(i32)]

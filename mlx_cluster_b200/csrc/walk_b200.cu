@@ -577,6 +577,25 @@ int walk_b200_csr_validate(const walk_b200_csr* g, const int64_t* start, int64_t
   return check_launch("csr_validate_kernel");
 }
 
+// ---- consumer of the walk matrix ----------------------------------------------------
+int walk_b200_context_windows(const int64_t* walks, int64_t num_walks, int32_t walk_length,
+                              int32_t context_size, int64_t* windows, void* stream) {
+  if (num_walks < 0 || walk_length < 0) return fail(WALK_B200_ERR_INVALID_ARG, "negative size");
+  if (context_size < 1 || context_size > walk_length + 1)
+    return fail(WALK_B200_ERR_INVALID_ARG, "context_size must be in [1, walk_length + 1] (got %d for walk_length %d)",
+                context_size, walk_length);
+  const int64_t nwin = (int64_t)walk_length + 2 - context_size;
+  const int64_t per_walk = nwin * context_size;
+  if (per_walk > 0x7fffffffll) return fail(WALK_B200_ERR_UNSUPPORTED, "one walk yields more than 2^31 window elements");
+  if (num_walks == 0) return WALK_B200_OK;
+  if (!walks || !windows) return fail(WALK_B200_ERR_INVALID_ARG, "walks or windows is NULL");
+  const int64_t bx = (per_walk + 2 * kBlock - 1) / (2 * kBlock);
+  dim3 grid((unsigned)(bx < 64 ? bx : 64), (unsigned)(num_walks < 65535 ? num_walks : 65535), 1);
+  context_windows_kernel<<<grid, kBlock, 0, (cudaStream_t)stream>>>(walks, num_walks, walk_length + 1, context_size,
+                                                                   (int32_t)per_walk, windows);
+  return check_launch("context_windows_kernel");
+}
+
 // ---- device probe -------------------------------------------------------------------
 int walk_b200_gather_probe(size_t array_bytes, int32_t iters, double* gathers_per_second) {
   if (!gathers_per_second || iters < 1 || array_bytes < (1u << 20))

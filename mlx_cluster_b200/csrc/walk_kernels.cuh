@@ -896,4 +896,39 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
   }
 }
 
+// ---------------------------------------------------------------------------------
+// context windows: the step after the walks in a node2vec pipeline
+// ---------------------------------------------------------------------------------
+// windows[(w * nwin + j) * cs + k] = walks[w * (L + 1) + j + k], nwin = L + 2 - cs: every run of cs
+// consecutive nodes of every walk (first column = centre node, the rest = its skip-gram context).
+// Streaming: each thread produces two adjacent output elements (one 16-byte store); the reads of
+// neighbouring threads overlap and are served by L1. 64-bit index arithmetic is done once per
+// walk row (blockIdx.y strides over walks), 32-bit inside a row.
+__global__ void __launch_bounds__(kBlock) context_windows_kernel(const int64_t* __restrict__ walks,
+                                                                 int64_t num_walks, int32_t row_len,
+                                                                 int32_t cs, int32_t per_walk,
+                                                                 int64_t* __restrict__ windows) {
+  for (int64_t w = blockIdx.y; w < num_walks; w += gridDim.y) {
+    const int64_t* __restrict__ row = walks + w * row_len;
+    int64_t* __restrict__ out = windows + w * (int64_t)per_walk;
+    for (int32_t f = 2 * (blockIdx.x * kBlock + threadIdx.x); f < per_walk; f += 2 * gridDim.x * kBlock) {
+      const int32_t j0 = f / cs, k0 = f - j0 * cs;
+      const int64_t a = __ldg(row + j0 + k0);
+      if (f + 1 < per_walk) {
+        int32_t j1 = j0, k1 = k0 + 1;
+        if (k1 == cs) { j1++; k1 = 0; }
+        const int64_t b = __ldg(row + j1 + k1);
+        if (((w * (int64_t)per_walk + f) & 1) == 0) {
+          *reinterpret_cast<longlong2*>(out + f) = make_longlong2(a, b);
+        } else {
+          out[f] = a;
+          out[f + 1] = b;
+        }
+      } else {
+        out[f] = a;
+      }
+    }
+  }
+}
+
 }  // namespace walk_b200

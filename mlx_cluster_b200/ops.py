@@ -21,7 +21,7 @@ import torch
 
 from . import _lib
 
-__all__ = ["random_walk", "rejection_sampling", "prepare_graph", "WalkGraph", "HostGraph",
+__all__ = ["random_walk", "rejection_sampling", "context_windows", "prepare_graph", "WalkGraph", "HostGraph",
            "read_status", "clear_caches"]
 
 
@@ -423,3 +423,28 @@ def _rejection_sampling_host(rowptr, col, start, L, p, q, seed, base, symmetric,
         _lib.check(_lib.lib().walk_b200_node2vec_walk_host(g._h, _ptr(start), n, L, p, q, int(seed) & (2**64 - 1),
                                                            int(base), int(stride), _ptr(out), _ptr(e_out)))
     return (out, e_out) if return_edges else out
+
+
+def context_windows(walks: torch.Tensor, context_size: int, *, stream=None, out: Optional[torch.Tensor] = None):
+    """All runs of ``context_size`` consecutive nodes of every walk: int64
+    ``[n * (walk_length + 2 - context_size), context_size]``, column 0 the centre node and the rest
+    its skip-gram context -- the input of node2vec's positive-pair loss. Same values as
+    ``walks.unfold(1, context_size, 1).reshape(-1, context_size)``, produced by one streaming kernel."""
+    _require(walks, "walks", torch.int64)
+    if not walks.is_cuda or walks.dim() != 2:
+        raise ValueError("walks must be a 2-D CUDA tensor [n, walk_length + 1]")
+    n, row = walks.shape
+    cs = int(context_size)
+    if cs < 1 or cs > row:
+        raise ValueError(f"context_size must be in [1, {row}]")
+    rows_out = n * (row + 1 - cs)
+    dev = walks.device
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty((rows_out, cs), dtype=torch.int64, device=dev)
+        else:
+            _require(out, "out", torch.int64, dev)
+            if out.numel() != rows_out * cs:
+                raise ValueError("out has the wrong size")
+        _lib.check(_lib.lib().walk_b200_context_windows(_ptr(walks), n, row - 1, cs, _ptr(out), _stream_handle(stream, dev)))
+    return out
