@@ -591,8 +591,16 @@ int walk_b200_context_windows(const int64_t* walks, int64_t num_walks, int32_t w
   if (!walks || !windows) return fail(WALK_B200_ERR_INVALID_ARG, "walks or windows is NULL");
   const int64_t bx = (per_walk + 2 * kBlock - 1) / (2 * kBlock);
   dim3 grid((unsigned)(bx < 64 ? bx : 64), (unsigned)(num_walks < 65535 ? num_walks : 65535), 1);
-  context_windows_kernel<<<grid, kBlock, 0, (cudaStream_t)stream>>>(walks, num_walks, walk_length + 1, context_size,
-                                                                   (int32_t)per_walk, windows);
+  // division by context_size as a multiply-high when that is exact for every element index of a walk
+  const uint64_t magic = (1ull << 32) / (uint64_t)context_size + 1;
+  const bool fast = magic <= 0xffffffffull &&
+                    (uint64_t)per_walk * (magic * (uint64_t)context_size - (1ull << 32)) < (1ull << 32);
+  if (fast)
+    context_windows_kernel<true><<<grid, kBlock, 0, (cudaStream_t)stream>>>(
+        walks, num_walks, walk_length + 1, context_size, (uint32_t)magic, (int32_t)per_walk, windows);
+  else
+    context_windows_kernel<false><<<grid, kBlock, 0, (cudaStream_t)stream>>>(
+        walks, num_walks, walk_length + 1, context_size, 0u, (int32_t)per_walk, windows);
   return check_launch("context_windows_kernel");
 }
 

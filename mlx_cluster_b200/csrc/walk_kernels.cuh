@@ -904,28 +904,34 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
 // Streaming: each thread produces two adjacent output elements (one 16-byte store); the reads of
 // neighbouring threads overlap and are served by L1. 64-bit index arithmetic is done once per
 // walk row (blockIdx.y strides over walks), 32-bit inside a row.
+// FAST_DIV: f / cs as a multiply-high with magic = floor(2^32 / cs) + 1, exact for every f the
+// launch can produce (the host checks per_walk * (magic * cs - 2^32) < 2^32 before choosing it).
+template <bool FAST_DIV>
 __global__ void __launch_bounds__(kBlock) context_windows_kernel(const int64_t* __restrict__ walks,
                                                                  int64_t num_walks, int32_t row_len,
-                                                                 int32_t cs, int32_t per_walk,
+                                                                 int32_t cs, uint32_t magic, int32_t per_walk,
                                                                  int64_t* __restrict__ windows) {
+  const L2Policy pol = make_policies(2);  // the windows stream out once: evict-first
   for (int64_t w = blockIdx.y; w < num_walks; w += gridDim.y) {
     const int64_t* __restrict__ row = walks + w * row_len;
     int64_t* __restrict__ out = windows + w * (int64_t)per_walk;
+    const bool aligned = ((w * (int64_t)per_walk) & 1) == 0;  // 16-byte alignment of this walk's output
     for (int32_t f = 2 * (blockIdx.x * kBlock + threadIdx.x); f < per_walk; f += 2 * gridDim.x * kBlock) {
-      const int32_t j0 = f / cs, k0 = f - j0 * cs;
+      const int32_t j0 = FAST_DIV ? (int32_t)__umulhi((uint32_t)f, magic) : f / cs;
+      const int32_t k0 = f - j0 * cs;
       const int64_t a = __ldg(row + j0 + k0);
       if (f + 1 < per_walk) {
         int32_t j1 = j0, k1 = k0 + 1;
         if (k1 == cs) { j1++; k1 = 0; }
         const int64_t b = __ldg(row + j1 + k1);
-        if (((w * (int64_t)per_walk + f) & 1) == 0) {
-          *reinterpret_cast<longlong2*>(out + f) = make_longlong2(a, b);
+        if (aligned) {
+          asm volatile("st.global.L2::cache_hint.v2.b64 [%0], {%1, %2}, %3;" ::"l"(out + f), "l"(a), "l"(b), "l"(pol.stream) : "memory");
         } else {
-          out[f] = a;
-          out[f + 1] = b;
+          st8(out + f, a, pol.stream);
+          st8(out + f + 1, b, pol.stream);
         }
       } else {
-        out[f] = a;
+        st8(out + f, a, pol.stream);
       }
     }
   }
