@@ -462,6 +462,7 @@ def run_ours(args, wl):
                 _lib.check(_lib.lib().walk_b200_uniform_walk_host(
                     hg._h, h_start.data_ptr(), h_rand.data_ptr(), rows, L, h_out.data_ptr(), None))
 
+        narrow = n_nodes < 2 ** 31 and _lib.get_tuning("host_narrow") != 0
         host_step()
         if barrier:
             barrier()
@@ -472,7 +473,10 @@ def run_ours(args, wl):
         e2e_ms = allmax(1e3 * dt / e2e_steps)
         e2e = {"value": walks_timed * L / (e2e_ms * 1e-3), "unit": "steps/s",
                "h2d_bytes_per_step": int(allsum(rows * 8 + (rows * L * 4 if rand is not None else 0))),
-               "d2h_bytes_per_step": int(allsum(rows * (L + 1) * 8)), "ms_per_step": e2e_ms, "steps": e2e_steps,
+               "d2h_bytes_per_step": int(allsum(rows * (L + 1) * (4 if narrow else 8))),
+               "ms_per_step": e2e_ms, "steps": e2e_steps,
+               "transport": "int32 on the bus, widened to the caller's int64 buffer by host threads" if narrow
+               else "int64",
                "api": "walk_b200_*_walk_host (C ABI, pinned host buffers, graph resident)",
                "graph_upload_s_once": upload_s}
         hg.close()

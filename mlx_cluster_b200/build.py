@@ -13,13 +13,13 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libwalk_b200.so"
-SOURCES = [CSRC / "walk_b200.cu"]
-HEADERS = [CSRC / "walk_kernels.cuh", CSRC / "philox.cuh", PKG.parent / "include" / "walk_b200.h"]
+SOURCES = [CSRC / "walk_b200.cu", CSRC / "host_widen.cpp"]
+HEADERS = [CSRC / "walk_kernels.cuh", CSRC / "philox.cuh", CSRC / "host_widen.h", PKG.parent / "include" / "walk_b200.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-lineinfo", "-O3", "-std=c++17",
-    "-Xcompiler", "-fPIC", "-shared",
+    "-Xcompiler", "-fPIC,-pthread", "-shared",
     "--fmad=false",  # the uniform walk's float32 product must not be contracted
 ]
 

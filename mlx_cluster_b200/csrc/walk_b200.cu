@@ -10,11 +10,14 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <memory>
 #include <mutex>
 #include <new>
 #include <string>
+#include <thread>
 
 #include "../../include/walk_b200.h"
+#include "host_widen.h"
 #include "walk_kernels.cuh"
 
 namespace {
@@ -66,6 +69,11 @@ struct Tuning {
   std::atomic<int32_t> l2_fetch_granularity{0};  // set only through walk_b200_set_tuning (applies the CUDA limit)
   std::atomic<int32_t> host_slab_mb{256};   // walk-matrix bytes per pipeline slab of the host entry points
   std::atomic<int32_t> use_rowdesc{1};      // host entry points: build and use the packed row descriptor
+  std::atomic<int32_t> host_narrow{1};      // host entry points: ids that fit int32 cross PCIe as int32
+  std::atomic<int32_t> host_threads{0};     // host threads that widen them again; 0 = min(16, hardware threads)
+  std::atomic<int32_t> host_single_launch{1};  // node2vec host entry: one launch over all rows, slabs copied out
+                                               // behind it as they complete (needs host_narrow)
+  std::atomic<int32_t> host_resident_mb{65536};  // ... while the int32 matrices fit this many MiB of device memory
 } g_tuning;
 
 std::atomic<int32_t>* tuning_slot(const char* key) {
@@ -83,6 +91,10 @@ std::atomic<int32_t>* tuning_slot(const char* key) {
   if (!strcmp(key, "l2_fetch_granularity")) return &g_tuning.l2_fetch_granularity;
   if (!strcmp(key, "host_slab_mb")) return &g_tuning.host_slab_mb;
   if (!strcmp(key, "use_rowdesc")) return &g_tuning.use_rowdesc;
+  if (!strcmp(key, "host_narrow")) return &g_tuning.host_narrow;
+  if (!strcmp(key, "host_threads")) return &g_tuning.host_threads;
+  if (!strcmp(key, "host_single_launch")) return &g_tuning.host_single_launch;
+  if (!strcmp(key, "host_resident_mb")) return &g_tuning.host_resident_mb;
   return nullptr;
 }
 
@@ -313,6 +325,74 @@ int launch_n2v(const Node2vecParams& P, bool sym, cudaStream_t s) {
   return launch_n2v_i<int64_t>(P, member, s);
 }
 
+// Single-launch mode of the host entry point: kernels that write int32 matrices and report finished
+// slabs. Built for 32-bit indices with row descriptors; returns kNoHostKernel for any other
+// configuration (the caller then runs the slab pipeline).
+constexpr int kNoHostKernel = -1;
+
+int launch_n2v_host(const Node2vecParams& P, bool sym, cudaStream_t s) {
+  const bool fits32 = P.num_nodes <= 0x7fffffffll && P.num_edges < 0x7fffffffll;
+  if (!fits32 || !P.desc || P.counters || g_tuning.n2v_idx.load() == 1) return kNoHostKernel;
+  const bool e = P.e_out != nullptr;
+  int member = sym ? MEMBER_SEARCH_PREV : MEMBER_SEARCH_CAND;
+  if (P.edgeset && P.edgeset_buckets > 0 && g_tuning.n2v_member.load() != 1) member = MEMBER_HASH;
+  if (member == MEMBER_HASH && P.revpos && rev_pays(P)) {
+    if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, true, false, true, true>, P, s);
+    return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, false, false, true, true>, P, s);
+  }
+  switch (member) {
+    case MEMBER_HASH:
+      if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, true, false, false, true>, P, s);
+      return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, false, false, false, true>, P, s);
+    case MEMBER_SEARCH_PREV:
+      if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_SEARCH_PREV, true, true, false, false, true>, P, s);
+      return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_SEARCH_PREV, true, false, false, false, true>, P, s);
+    default:
+      if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_SEARCH_CAND, true, true, false, false, true>, P, s);
+      return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_SEARCH_CAND, true, false, false, false, true>, P, s);
+  }
+}
+
+// Argument checks and kernel parameters shared by the device-pointer entry and the host entry.
+int prepare_n2v(const walk_b200_csr* g, const int64_t* start, int64_t num_walks, int32_t walk_length,
+                double p, double q, uint64_t seed, uint64_t walk_index_base, uint64_t walk_index_stride,
+                int64_t* n_out, int64_t* e_out, uint32_t* status_flags, uint64_t* counters,
+                Node2vecParams* out) {
+  if (int rc = check_csr(g)) return rc;
+  if (int rc = check_walk_sizes(num_walks, walk_length, start, n_out)) return rc;
+  double prob[3];
+  uint32_t cuts[3];
+  if (int rc = thresholds(p, q, prob, cuts)) return rc;
+  Node2vecParams P{};
+  P.rowptr = g->rowptr; P.col = g->col; P.desc = g->rowdesc;
+  P.num_nodes = g->num_nodes; P.num_edges = g->num_edges;
+  P.start = start; P.num_walks = num_walks; P.walk_length = walk_length;
+  P.cut0 = cuts[0]; P.cut1 = cuts[1]; P.cut2 = cuts[2];
+  P.key0 = (uint32_t)seed; P.key1 = (uint32_t)(seed >> 32);
+  P.walk_index_base = walk_index_base;
+  P.walk_index_stride = walk_index_stride ? walk_index_stride : 1;
+  P.max_attempts = WALK_B200_MAX_ATTEMPTS;
+  P.batch_lanes = g_tuning.n2v_batch_lanes.load();
+  P.batch_trips = g_tuning.n2v_batch_trips.load();
+  if (P.batch_lanes < 1) P.batch_lanes = 1;
+  if (P.batch_trips < 1) P.batch_trips = 1;
+  P.draw_loop = g_tuning.n2v_draw_loop.load();
+  if (P.draw_loop < 1) P.draw_loop = 1;
+  P.n_out = n_out; P.e_out = walk_length > 0 ? e_out : nullptr;
+  P.flags = status_flags; P.counters = (unsigned long long*)counters;
+  P.hints = g_tuning.l2_hints.load();
+  if (g->edgeset && g->edgeset_buckets > 0) {
+    if (g->num_nodes >= 0xffffffffll)
+      return fail(WALK_B200_ERR_UNSUPPORTED, "the edge hash set needs num_nodes < 2^32 - 1");
+    if ((reinterpret_cast<uintptr_t>(g->edgeset) & 31) != 0)
+      return fail(WALK_B200_ERR_INVALID_ARG, "edgeset must be 32-byte aligned");
+    P.edgeset = g->edgeset; P.edgeset_buckets = g->edgeset_buckets;
+    P.revpos = g->revpos;
+  }
+  *out = P;
+  return WALK_B200_OK;
+}
+
 int grid_for_streaming(int64_t n) {
   int64_t b = blocks_for(n);
   const int64_t cap = 148 * 16;  // 16 resident blocks' worth per SM of a 148-SM part
@@ -470,38 +550,11 @@ int walk_b200_node2vec_walk(const walk_b200_csr* g, const int64_t* start, int64_
                             int32_t walk_length, double p, double q, uint64_t seed,
                             uint64_t walk_index_base, uint64_t walk_index_stride, int64_t* n_out,
                             int64_t* e_out, uint32_t* status_flags, uint64_t* counters, void* stream) {
-  if (int rc = check_csr(g)) return rc;
-  if (int rc = check_walk_sizes(num_walks, walk_length, start, n_out)) return rc;
-  double prob[3];
-  uint32_t cuts[3];
-  if (int rc = thresholds(p, q, prob, cuts)) return rc;
-  if (num_walks == 0) return WALK_B200_OK;
   Node2vecParams P{};
-  P.rowptr = g->rowptr; P.col = g->col; P.desc = g->rowdesc;
-  P.num_nodes = g->num_nodes; P.num_edges = g->num_edges;
-  P.start = start; P.num_walks = num_walks; P.walk_length = walk_length;
-  P.cut0 = cuts[0]; P.cut1 = cuts[1]; P.cut2 = cuts[2];
-  P.key0 = (uint32_t)seed; P.key1 = (uint32_t)(seed >> 32);
-  P.walk_index_base = walk_index_base;
-  P.walk_index_stride = walk_index_stride ? walk_index_stride : 1;
-  P.max_attempts = WALK_B200_MAX_ATTEMPTS;
-  P.batch_lanes = g_tuning.n2v_batch_lanes.load();
-  P.batch_trips = g_tuning.n2v_batch_trips.load();
-  if (P.batch_lanes < 1) P.batch_lanes = 1;
-  if (P.batch_trips < 1) P.batch_trips = 1;
-  P.draw_loop = g_tuning.n2v_draw_loop.load();
-  if (P.draw_loop < 1) P.draw_loop = 1;
-  P.n_out = n_out; P.e_out = walk_length > 0 ? e_out : nullptr;
-  P.flags = status_flags; P.counters = (unsigned long long*)counters;
-  P.hints = g_tuning.l2_hints.load();
-  if (g->edgeset && g->edgeset_buckets > 0) {
-    if (g->num_nodes >= 0xffffffffll)
-      return fail(WALK_B200_ERR_UNSUPPORTED, "the edge hash set needs num_nodes < 2^32 - 1");
-    if ((reinterpret_cast<uintptr_t>(g->edgeset) & 31) != 0)
-      return fail(WALK_B200_ERR_INVALID_ARG, "edgeset must be 32-byte aligned");
-    P.edgeset = g->edgeset; P.edgeset_buckets = g->edgeset_buckets;
-    P.revpos = g->revpos;
-  }
+  if (int rc = prepare_n2v(g, start, num_walks, walk_length, p, q, seed, walk_index_base, walk_index_stride,
+                           n_out, e_out, status_flags, counters, &P))
+    return rc;
+  if (num_walks == 0) return WALK_B200_OK;
   return launch_n2v(P, (g->flags & WALK_B200_CSR_SYMMETRIC) != 0, (cudaStream_t)stream);
 }
 
@@ -782,13 +835,28 @@ struct walk_b200_graph {
   uint32_t* d_revpos = nullptr;
   void* d_fused = nullptr;
   uint32_t* d_flags = nullptr;
-  static constexpr int kLanes = 3;  // slabs in flight: copy-in, kernel, copy-out
+  static constexpr int kLanes = 4;  // slabs in flight: copy-in, kernel, copy-out, host widening
   cudaStream_t streams[kLanes] = {};
+  cudaEvent_t landed[kLanes] = {};  // narrow transport: the slab's int32 copy is in host staging
   int64_t* d_start[kLanes] = {};
   float* d_rand[kLanes] = {};
   int64_t* d_out[kLanes] = {};
   int64_t* d_eout[kLanes] = {};
+  int32_t* d_pack[kLanes] = {};     // narrow transport: int32 copies of d_out / d_eout ...
+  int32_t* d_epack[kLanes] = {};
+  int32_t* h_pack[kLanes] = {};     // ... and their pinned host staging
+  int32_t* h_epack[kLanes] = {};
   size_t cap_start = 0, cap_rand = 0, cap_out = 0, cap_eout = 0;  // bytes per lane
+  size_t cap_pack = 0, cap_epack = 0, cap_hpack = 0, cap_hepack = 0;
+  // single-launch mode of the node2vec host entry: all start rows, the whole int32 walk (and edge)
+  // matrix, per-slab counters of finished walks, and the per-slab flags the kernel sets (mapped host memory)
+  int64_t* d_start_all = nullptr;
+  int32_t* d_all = nullptr;
+  int32_t* d_eall = nullptr;
+  uint32_t* d_slab_done = nullptr;
+  uint32_t* h_slab_flags = nullptr;
+  size_t cap_start_all = 0, cap_all = 0, cap_eall = 0, cap_slab_done = 0, cap_slab_flags = 0;
+  std::unique_ptr<WidenPool> pool;
   std::mutex mu;
 };
 
@@ -818,6 +886,49 @@ int grow(T** bufs, size_t* cap, size_t need) {
   return WALK_B200_OK;
 }
 
+int grow_pinned(int32_t** bufs, size_t* cap, size_t need) {
+  if (need <= *cap) return WALK_B200_OK;
+  for (int k = 0; k < walk_b200_graph::kLanes; k++) {
+    if (bufs[k]) cudaFreeHost(bufs[k]);
+    bufs[k] = nullptr;
+  }
+  *cap = 0;
+  for (int k = 0; k < walk_b200_graph::kLanes; k++) CUDA_TRY(cudaHostAlloc((void**)&bufs[k], need, cudaHostAllocDefault));
+  *cap = need;
+  return WALK_B200_OK;
+}
+
+template <typename T>
+int grow_one(T** buf, size_t* cap, size_t need) {
+  if (need <= *cap) return WALK_B200_OK;
+  if (*buf) cudaFree(*buf);
+  *buf = nullptr;
+  *cap = 0;
+  CUDA_TRY(cudaMalloc((void**)buf, need));
+  *cap = need;
+  return WALK_B200_OK;
+}
+
+int ensure_pool(walk_b200_graph* g) {
+  int want_threads = g_tuning.host_threads.load();
+  if (want_threads <= 0) {
+    want_threads = (int)std::thread::hardware_concurrency();
+    if (want_threads > 16) want_threads = 16;
+    if (want_threads < 1) want_threads = 1;
+  }
+  if (!g->pool || g->pool->workers() != want_threads - 1) g->pool.reset(new WidenPool(want_threads - 1));
+  return WALK_B200_OK;
+}
+
+int launch_narrow(const int64_t* in, int64_t count, int32_t* out, cudaStream_t s) {
+  if (count <= 0) return WALK_B200_OK;
+  int64_t blocks = blocks_for((count + 3) / 4);
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  narrow_i64_kernel<<<(unsigned)blocks, kBlock, 0, s>>>(in, count, out);
+  return check_launch("narrow_i64_kernel");
+}
+
 int flags_to_status(uint32_t f) {
   if (!f) return WALK_B200_OK;
   return fail(WALK_B200_ERR_DEVICE_FLAGS,
@@ -831,9 +942,119 @@ int flags_to_status(uint32_t f) {
               (f & WALK_B200_FLAG_EDGESET_FULL) ? " edge hash set overflow;" : "");
 }
 
+// node2vec over host buffers as ONE launch: all start rows go up, the kernel writes int32 matrices
+// that stay on the device, counts finished walks per slab of 2^shift rows and sets a flag in mapped
+// host memory when a slab is complete. The host copies each complete slab into pinned staging on a
+// second stream while the launch goes on, and widens it into the caller's int64 buffers. Against
+// one launch per slab this removes the drain at the end of every launch (each costs about as long
+// as the slowest walk of the slab; consecutive launches of a persistent kernel barely overlap).
+// The kernel never waits for the host. Returns kNoHostKernel (before doing anything) when this
+// mode does not apply; the caller then runs the slab pipeline. Called with g->mu held and the
+// graph's device current.
+int run_host_n2v_single(walk_b200_graph* g, const walk_b200_csr& csr, const int64_t* h_start, int64_t n, int32_t L,
+                        double p, double q, uint64_t seed, uint64_t base, uint64_t stride, int64_t* h_n_out,
+                        int64_t* h_e_out) {
+  constexpr int kLanes = walk_b200_graph::kLanes;
+  const bool want_e = h_e_out && L > 0;
+  if (!g->d_desc || g->num_nodes >= (1ll << 31) || g->num_edges >= (1ll << 31) - 1) return kNoHostKernel;
+  const size_t row32 = (size_t)(L + 1) * 4;
+  const size_t need = (size_t)n * row32 + (want_e ? (size_t)n * L * 4 : 0);
+  if (need > ((size_t)g_tuning.host_resident_mb.load() << 20)) return kNoHostKernel;
+  if (g_tuning.n2v_idx.load() == 1) return kNoHostKernel;
+
+  // slab: the largest power of two of rows whose int32 copy is at most a quarter of the slab tuning
+  int shift = 10;
+  const size_t target = ((size_t)g_tuning.host_slab_mb.load() << 20) / 4;
+  while (shift < 30 && ((size_t)2 << shift) * row32 <= target) shift++;
+  const int64_t slab_rows = (int64_t)1 << shift;
+  const int64_t slabs = (n + slab_rows - 1) / slab_rows;
+
+  if (int rc = grow_one(&g->d_start_all, &g->cap_start_all, (size_t)n * 8)) return rc;
+  if (int rc = grow_one(&g->d_all, &g->cap_all, (size_t)n * row32)) return rc;
+  if (want_e) if (int rc = grow_one(&g->d_eall, &g->cap_eall, (size_t)n * L * 4)) return rc;
+  if (int rc = grow_one(&g->d_slab_done, &g->cap_slab_done, (size_t)slabs * 4)) return rc;
+  if ((size_t)slabs * 4 > g->cap_slab_flags) {
+    if (g->h_slab_flags) cudaFreeHost(g->h_slab_flags);
+    g->h_slab_flags = nullptr;
+    g->cap_slab_flags = 0;
+    CUDA_TRY(cudaHostAlloc((void**)&g->h_slab_flags, (size_t)slabs * 4, cudaHostAllocMapped));
+    g->cap_slab_flags = (size_t)slabs * 4;
+  }
+  const size_t slab_bytes = (size_t)(slab_rows < n ? slab_rows : n) * row32;
+  if (int rc = grow_pinned(g->h_pack, &g->cap_hpack, slab_bytes)) return rc;
+  if (want_e) if (int rc = grow_pinned(g->h_epack, &g->cap_hepack, (size_t)(slab_rows < n ? slab_rows : n) * L * 4)) return rc;
+  if (int rc = ensure_pool(g)) return rc;
+  uint32_t* d_slab_flags = nullptr;
+  CUDA_TRY(cudaHostGetDevicePointer((void**)&d_slab_flags, g->h_slab_flags, 0));
+
+  cudaStream_t work = g->streams[0], copy = g->streams[1];
+  volatile uint32_t* flags = g->h_slab_flags;
+  for (int64_t k = 0; k < slabs; k++) flags[k] = 0;
+  CUDA_TRY(cudaMemsetAsync(g->d_flags, 0, sizeof(uint32_t), work));
+  CUDA_TRY(cudaMemsetAsync(g->d_slab_done, 0, (size_t)slabs * 4, work));
+  CUDA_TRY(cudaMemcpyAsync(g->d_start_all, h_start, (size_t)n * 8, cudaMemcpyHostToDevice, work));
+
+  Node2vecParams P{};
+  if (int rc = prepare_n2v(&csr, g->d_start_all, n, L, p, q, seed, base, stride, reinterpret_cast<int64_t*>(g->d_all),
+                           want_e ? reinterpret_cast<int64_t*>(g->d_eall) : nullptr, g->d_flags, nullptr, &P))
+    return rc;
+  P.slab_shift = shift;
+  P.slab_done = g->d_slab_done;
+  P.slab_flags = d_slab_flags;
+  {
+    const int rc = launch_n2v_host(P, (csr.flags & WALK_B200_CSR_SYMMETRIC) != 0, work);
+    if (rc == kNoHostKernel) {  // nothing was launched; leave the stream idle for the fallback
+      CUDA_TRY(cudaStreamSynchronize(work));
+      return kNoHostKernel;
+    }
+    if (rc) return rc;
+  }
+
+  auto rows_of = [&](int64_t k) { return (n - k * slab_rows < slab_rows) ? n - k * slab_rows : slab_rows; };
+  auto widen = [&](int64_t k) -> int {
+    const int lane = (int)(k % kLanes);
+    CUDA_TRY(cudaEventSynchronize(g->landed[lane]));
+    g->pool->widen(g->h_pack[lane], h_n_out + k * slab_rows * (L + 1), rows_of(k) * (L + 1));
+    if (want_e) g->pool->widen(g->h_epack[lane], h_e_out + k * slab_rows * L, rows_of(k) * L);
+    return WALK_B200_OK;
+  };
+
+  bool kernel_done = false;
+  for (int64_t k = 0; k < slabs; k++) {
+    // Wait for the slab's flag. The launch is finite (every walk has an attempt cap), so the wait
+    // ends at the latest when the work stream has drained; then every slab is complete.
+    for (uint32_t spins = 0; !kernel_done && flags[k] == 0; spins++) {
+      if ((spins & 63) == 63) {
+        const cudaError_t st = cudaStreamQuery(work);
+        if (st == cudaSuccess) kernel_done = true;
+        else if (st != cudaErrorNotReady) return fail(WALK_B200_ERR_CUDA, "node2vec launch failed: %s", cudaGetErrorString(st));
+      }
+      std::this_thread::yield();
+    }
+    const int lane = (int)(k % kLanes);
+    // the lane's staging was widened kLanes - 1 slabs ago (the widen below trails by one slab)
+    CUDA_TRY(cudaMemcpyAsync(g->h_pack[lane], g->d_all + k * slab_rows * (L + 1), (size_t)rows_of(k) * row32,
+                             cudaMemcpyDeviceToHost, copy));
+    if (want_e)
+      CUDA_TRY(cudaMemcpyAsync(g->h_epack[lane], g->d_eall + k * slab_rows * L, (size_t)rows_of(k) * L * 4,
+                               cudaMemcpyDeviceToHost, copy));
+    CUDA_TRY(cudaEventRecord(g->landed[lane], copy));
+    if (k >= 1) if (int rc = widen(k - 1)) return rc;
+  }
+  if (int rc = widen(slabs - 1)) return rc;
+  CUDA_TRY(cudaStreamSynchronize(work));
+  CUDA_TRY(cudaStreamSynchronize(copy));
+  uint32_t f = 0;
+  CUDA_TRY(cudaMemcpy(&f, g->d_flags, sizeof(f), cudaMemcpyDeviceToHost));
+  return flags_to_status(f);
+}
+
 // Runs one walk over host buffers in slabs: H2D(start[, rand]) -> kernel -> D2H(walks)
 // per slab, slabs round-robin over kLanes streams so copies in both directions overlap
-// the kernels of neighbouring slabs.
+// the kernels of neighbouring slabs. When every id fits int32 (and the tuning allows it) the
+// slab is packed to int32 on the device, lands in pinned staging owned by the graph and is widened
+// into the caller's buffer by host threads while later slabs run: half the bytes on the bus, and
+// the caller's output buffers need not be pinned.
 int run_host_walk(walk_b200_graph* g, bool biased, const int64_t* h_start, const float* h_rand,
                   int64_t n, int32_t L, double p, double q, uint64_t seed, uint64_t base, uint64_t stride,
                   int64_t* h_n_out, int64_t* h_e_out) {
@@ -850,6 +1071,22 @@ int run_host_walk(walk_b200_graph* g, bool biased, const int64_t* h_start, const
   DeviceGuard dg(g->device);
   if (!dg.ok) return fail(WALK_B200_ERR_CUDA, "cannot select device %d", g->device);
 
+  constexpr int kLanes = walk_b200_graph::kLanes;
+  const bool want_e = h_e_out && L > 0;
+  const bool narrow = g_tuning.host_narrow.load() != 0 && g->num_nodes < (1ll << 31) &&
+                      (!want_e || g->num_edges < (1ll << 31));
+  walk_b200_csr csr{};
+  csr.rowptr = g->d_rowptr; csr.col = g->d_col; csr.num_nodes = g->num_nodes; csr.num_edges = g->num_edges;
+  csr.rowdesc = g->d_desc; csr.flags = g->csr_flags;
+  csr.edgeset = g->d_edgeset; csr.edgeset_buckets = g->edgeset_buckets;
+  csr.revpos = g->d_revpos;
+  csr.fused = g->d_fused;
+
+  if (biased && narrow && g_tuning.host_single_launch.load() != 0) {
+    const int rc = run_host_n2v_single(g, csr, h_start, n, L, p, q, seed, base, stride, h_n_out, h_e_out);
+    if (rc != kNoHostKernel) return rc;
+  }
+
   const size_t row_bytes = (size_t)(L + 1) * 8;
   int64_t slab_rows = (int64_t)(((size_t)g_tuning.host_slab_mb.load() << 20) / row_bytes);
   if (slab_rows < 1024) slab_rows = 1024;
@@ -858,24 +1095,40 @@ int run_host_walk(walk_b200_graph* g, bool biased, const int64_t* h_start, const
   if (int rc = grow(g->d_start, &g->cap_start, (size_t)slab_rows * 8)) return rc;
   if (int rc = grow(g->d_out, &g->cap_out, (size_t)slab_rows * row_bytes)) return rc;
   if (!biased && L > 0) if (int rc = grow(g->d_rand, &g->cap_rand, (size_t)slab_rows * L * 4)) return rc;
-  if (h_e_out && L > 0) if (int rc = grow(g->d_eout, &g->cap_eout, (size_t)slab_rows * L * 8)) return rc;
+  if (want_e) if (int rc = grow(g->d_eout, &g->cap_eout, (size_t)slab_rows * L * 8)) return rc;
+  if (narrow) {
+    if (int rc = grow(g->d_pack, &g->cap_pack, (size_t)slab_rows * row_bytes / 2)) return rc;
+    if (int rc = grow_pinned(g->h_pack, &g->cap_hpack, (size_t)slab_rows * row_bytes / 2)) return rc;
+    if (want_e) {
+      if (int rc = grow(g->d_epack, &g->cap_epack, (size_t)slab_rows * L * 4)) return rc;
+      if (int rc = grow_pinned(g->h_epack, &g->cap_hepack, (size_t)slab_rows * L * 4)) return rc;
+    }
+    if (int rc = ensure_pool(g)) return rc;
+  }
 
   CUDA_TRY(cudaMemsetAsync(g->d_flags, 0, sizeof(uint32_t), g->streams[0]));
   CUDA_TRY(cudaStreamSynchronize(g->streams[0]));
 
-  walk_b200_csr csr{};
-  csr.rowptr = g->d_rowptr; csr.col = g->d_col; csr.num_nodes = g->num_nodes; csr.num_edges = g->num_edges;
-  csr.rowdesc = g->d_desc; csr.flags = g->csr_flags;
-  csr.edgeset = g->d_edgeset; csr.edgeset_buckets = g->edgeset_buckets;
-  csr.revpos = g->d_revpos;
-  csr.fused = g->d_fused;
+  // widen slab `i` (narrow transport) once its staging copy has landed
+  auto finish = [&](int64_t i) -> int {
+    const int lane = (int)(i % kLanes);
+    const int64_t r0 = i * slab_rows;
+    const int64_t rows = (n - r0 < slab_rows) ? n - r0 : slab_rows;
+    CUDA_TRY(cudaEventSynchronize(g->landed[lane]));
+    g->pool->widen(g->h_pack[lane], h_n_out + r0 * (L + 1), rows * (L + 1));
+    if (want_e) g->pool->widen(g->h_epack[lane], h_e_out + r0 * L, rows * L);
+    return WALK_B200_OK;
+  };
 
-  int lane = 0;
-  for (int64_t r0 = 0; r0 < n; r0 += slab_rows, lane = (lane + 1) % walk_b200_graph::kLanes) {
+  const int64_t slabs = (n + slab_rows - 1) / slab_rows;
+  constexpr int64_t kLag = kLanes - 1;  // slabs queued on the device while the host widens an older one
+  for (int64_t i = 0; i < slabs; i++) {
+    const int lane = (int)(i % kLanes);
+    const int64_t r0 = i * slab_rows;
     const int64_t rows = (n - r0 < slab_rows) ? n - r0 : slab_rows;
     cudaStream_t s = g->streams[lane];
     CUDA_TRY(cudaMemcpyAsync(g->d_start[lane], h_start + r0, (size_t)rows * 8, cudaMemcpyHostToDevice, s));
-    int64_t* d_e = (h_e_out && L > 0) ? g->d_eout[lane] : nullptr;
+    int64_t* d_e = want_e ? g->d_eout[lane] : nullptr;
     int rc;
     if (biased) {
       rc = walk_b200_node2vec_walk(&csr, g->d_start[lane], rows, L, p, q, seed, base + (uint64_t)r0 * stride,
@@ -887,10 +1140,24 @@ int run_host_walk(walk_b200_graph* g, bool biased, const int64_t* h_start, const
                                   g->d_flags, s);
     }
     if (rc) return rc;
-    CUDA_TRY(cudaMemcpyAsync(h_n_out + r0 * (L + 1), g->d_out[lane], (size_t)rows * row_bytes, cudaMemcpyDeviceToHost, s));
-    if (d_e) CUDA_TRY(cudaMemcpyAsync(h_e_out + r0 * L, d_e, (size_t)rows * L * 8, cudaMemcpyDeviceToHost, s));
+    if (narrow) {
+      if (int rc2 = launch_narrow(g->d_out[lane], rows * (L + 1), g->d_pack[lane], s)) return rc2;
+      CUDA_TRY(cudaMemcpyAsync(g->h_pack[lane], g->d_pack[lane], (size_t)rows * (L + 1) * 4, cudaMemcpyDeviceToHost, s));
+      if (d_e) {
+        if (int rc2 = launch_narrow(d_e, rows * L, g->d_epack[lane], s)) return rc2;
+        CUDA_TRY(cudaMemcpyAsync(g->h_epack[lane], g->d_epack[lane], (size_t)rows * L * 4, cudaMemcpyDeviceToHost, s));
+      }
+      CUDA_TRY(cudaEventRecord(g->landed[lane], s));
+      if (i >= kLag) if (int rc2 = finish(i - kLag)) return rc2;  // frees the lane slab i + 1 will use
+    } else {
+      CUDA_TRY(cudaMemcpyAsync(h_n_out + r0 * (L + 1), g->d_out[lane], (size_t)rows * row_bytes, cudaMemcpyDeviceToHost, s));
+      if (d_e) CUDA_TRY(cudaMemcpyAsync(h_e_out + r0 * L, d_e, (size_t)rows * L * 8, cudaMemcpyDeviceToHost, s));
+    }
   }
-  for (int k = 0; k < walk_b200_graph::kLanes; k++) CUDA_TRY(cudaStreamSynchronize(g->streams[k]));
+  if (narrow)
+    for (int64_t i = (slabs > kLag ? slabs - kLag : 0); i < slabs; i++)
+      if (int rc2 = finish(i)) return rc2;
+  for (int k = 0; k < kLanes; k++) CUDA_TRY(cudaStreamSynchronize(g->streams[k]));
   uint32_t f = 0;
   CUDA_TRY(cudaMemcpy(&f, g->d_flags, sizeof(f), cudaMemcpyDeviceToHost));
   return flags_to_status(f);
@@ -917,7 +1184,10 @@ int walk_b200_graph_create(const int64_t* h_rowptr, const int64_t* h_col, int64_
   } while (0)
   G_TRY(cudaGetDevice(&g->device));
   g->num_nodes = num_nodes; g->num_edges = num_edges; g->csr_flags = csr_flags;
-  for (int k = 0; k < walk_b200_graph::kLanes; k++) G_TRY(cudaStreamCreateWithFlags(&g->streams[k], cudaStreamNonBlocking));
+  for (int k = 0; k < walk_b200_graph::kLanes; k++) {
+    G_TRY(cudaStreamCreateWithFlags(&g->streams[k], cudaStreamNonBlocking));
+    G_TRY(cudaEventCreateWithFlags(&g->landed[k], cudaEventDisableTiming));
+  }
   G_TRY(cudaMalloc((void**)&g->d_rowptr, (size_t)(num_nodes + 1) * 8));
   G_TRY(cudaMalloc((void**)&g->d_col, (size_t)(num_edges > 0 ? num_edges : 1) * 8));
   G_TRY(cudaMalloc((void**)&g->d_flags, 256));
@@ -993,6 +1263,11 @@ int walk_b200_graph_destroy(walk_b200_graph* g) {
       if (g->d_rand[k]) cudaFree(g->d_rand[k]);
       if (g->d_out[k]) cudaFree(g->d_out[k]);
       if (g->d_eout[k]) cudaFree(g->d_eout[k]);
+      if (g->d_pack[k]) cudaFree(g->d_pack[k]);
+      if (g->d_epack[k]) cudaFree(g->d_epack[k]);
+      if (g->h_pack[k]) cudaFreeHost(g->h_pack[k]);
+      if (g->h_epack[k]) cudaFreeHost(g->h_epack[k]);
+      if (g->landed[k]) cudaEventDestroy(g->landed[k]);
     }
     if (g->d_rowptr) cudaFree(g->d_rowptr);
     if (g->d_col) cudaFree(g->d_col);
@@ -1001,6 +1276,11 @@ int walk_b200_graph_destroy(walk_b200_graph* g) {
     if (g->d_revpos) cudaFree(g->d_revpos);
     if (g->d_fused) cudaFree(g->d_fused);
     if (g->d_flags) cudaFree(g->d_flags);
+    if (g->d_start_all) cudaFree(g->d_start_all);
+    if (g->d_all) cudaFree(g->d_all);
+    if (g->d_eall) cudaFree(g->d_eall);
+    if (g->d_slab_done) cudaFree(g->d_slab_done);
+    if (g->h_slab_flags) cudaFreeHost(g->h_slab_flags);
   }
   delete g;
   return WALK_B200_OK;

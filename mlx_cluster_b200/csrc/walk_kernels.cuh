@@ -544,6 +544,13 @@ struct Node2vecParams {
   uint32_t* flags;
   unsigned long long* counters;
   unsigned long long* queue;  // launch-wide chunk counter, zero at launch
+  // HOST kernels only: n_out / e_out point at int32 matrices; finished walks are counted per slab of
+  // 2^slab_shift consecutive rows in slab_done (zero at launch); the walk that completes a slab sets
+  // slab_flags[slab] (mapped host memory), after which the host may copy that slab's rows out while
+  // the launch goes on.
+  int32_t slab_shift;
+  uint32_t* slab_done;
+  volatile uint32_t* slab_flags;
 };
 
 enum : int { ST_IDLE = 0, ST_START, ST_ROW, ST_ACCEPTED, ST_ATTEMPT, ST_XROW, ST_SEARCH, ST_HASH };
@@ -584,7 +591,11 @@ enum : int { MEMBER_SEARCH_PREV = 0, MEMBER_SEARCH_CAND = 1, MEMBER_HASH = 2 };
 // gather, and an attempt whose accept draw is >= cut1 can only be accepted by the return rule:
 // if its edge is not ret_e it is rejected without touching memory at all. At (p, q) = (0.25, 4)
 // that is three attempts in four. Same draws, same decisions, fewer gathers.
-template <typename idx_t, int MEMBER, bool USE_DESC, bool HAS_EOUT, bool COUNT, bool REV = false>
+//
+// HOST (the host-buffer entry point's single-launch mode): the walk and edge matrices are int32
+// (P.n_out / P.e_out point at int32 storage; the ids fit) and finished walks are counted per slab of
+// 2^slab_shift rows, so the host can copy a slab out as soon as its last walk is done.
+template <typename idx_t, int MEMBER, bool USE_DESC, bool HAS_EOUT, bool COUNT, bool REV = false, bool HOST = false>
 __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(const Node2vecParams P) {
   static_assert(!REV || (MEMBER == MEMBER_HASH && USE_DESC && sizeof(idx_t) == 4), "REV needs hash membership, row descriptors, 32-bit indices");
   constexpr unsigned kFull = 0xffffffffu;
@@ -616,8 +627,30 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
   int32_t l = 0;                  // step being produced
   uint32_t a = 0;                 // attempt counter of this step
   int state = ST_IDLE;
+  bool finished = false;          // the lane completed a walk in the last trip (progress reporting)
+
+  auto put_node = [&](int64_t row, int32_t k, int64_t node) {
+    if (HOST) reinterpret_cast<int32_t*>(P.n_out)[row * ((int64_t)L + 1) + k] = (int32_t)node;
+    else st8(P.n_out + row * ((int64_t)L + 1) + k, node, pol.stream);
+  };
+  auto put_edge = [&](int64_t row, int32_t k, int64_t edge) {
+    if (HOST) reinterpret_cast<int32_t*>(P.e_out)[row * (int64_t)L + k] = (int32_t)edge;
+    else P.e_out[row * (int64_t)L + k] = edge;
+  };
 
   while (true) {
+    // ---- progress reporting: a finished walk's rows are made visible, then counted for its slab
+    if (HOST && finished) {
+      __threadfence();
+      const int64_t slab = i >> P.slab_shift;
+      const int64_t rows_in_slab = min((int64_t)1 << P.slab_shift, n - (slab << P.slab_shift));
+      if ((int64_t)atomicAdd(P.slab_done + slab, 1u) + 1 == rows_in_slab) {
+        __threadfence_system();
+        P.slab_flags[slab] = 1u;
+      }
+    }
+    if (HOST) finished = false;
+
     // ---- hand walks to idle lanes (all lanes of the warp pass here together)
     const unsigned idle = __ballot_sync(kFull, state == ST_IDLE);
     if (idle) {
@@ -667,13 +700,12 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
       bool need_load = true;  // REV: some attempts are decided without touching memory
 
       if (state == ST_ACCEPTED) {  // write the decided step, advance, go on to the next row fetch
-        int64_t* out = P.n_out + i * ((int64_t)L + 1);
-        st8(out + l + 1, (int64_t)x, pol.stream);
-        if (HAS_EOUT) P.e_out[i * (int64_t)L + l] = (a >= P.max_attempts) ? -1 : (int64_t)e;
+        put_node(i, l + 1, (int64_t)x);
+        if (HAS_EOUT) put_edge(i, l, (a >= P.max_attempts) ? -1 : (int64_t)e);
         t = v; t_rs = v_rs; t_re = v_re;
         v = x;
         l++;
-        if (l == L) { state = ST_IDLE; need_load = false; }
+        if (l == L) { state = ST_IDLE; finished = true; need_load = false; }
         else state = ST_ROW;
       }
 
@@ -767,17 +799,20 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
       if (!need_load) {
         // nothing was loaded
       } else if (state == ST_START) {
-        int64_t* out = P.n_out + i * ((int64_t)L + 1);
-        out[0] = val;
+        put_node(i, 0, val);
         t = (idx_t)val;
         v = (idx_t)val;
         l = 0;
         if ((uint64_t)val >= (uint64_t)P.num_nodes) {
           raise_flag(P.flags, WALK_B200_FLAG_BAD_NODE);
-          for (int32_t k = 0; k < L; k++) { out[k + 1] = val; if (HAS_EOUT) P.e_out[i * (int64_t)L + k] = -1; }
+          for (int32_t k = 0; k < L; k++) { put_node(i, k + 1, val); if (HAS_EOUT) put_edge(i, k, -1); }
           state = ST_IDLE;
+          finished = true;
+        } else if (L > 0) {
+          state = ST_ROW;
         } else {
-          state = L > 0 ? ST_ROW : ST_IDLE;
+          state = ST_IDLE;
+          finished = true;
         }
       } else if (state == ST_ROW || state == ST_XROW) {
         int64_t rs, deg;
@@ -788,9 +823,9 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
           if (deg == 0) {
             // stay in place for every remaining step
             if (COUNT) c_deg0 += (uint32_t)(L - l);
-            int64_t* out = P.n_out + i * ((int64_t)L + 1);
-            for (int32_t k = l; k < L; k++) { st8(out + k + 1, (int64_t)v, pol.stream); if (HAS_EOUT) P.e_out[i * (int64_t)L + k] = -1; }
+            for (int32_t k = l; k < L; k++) { put_node(i, k + 1, (int64_t)v); if (HAS_EOUT) put_edge(i, k, -1); }
             state = ST_IDLE;
+            finished = true;
           } else {
             v_rs = (idx_t)rs;
             v_re = (idx_t)(rs + deg);
@@ -935,6 +970,22 @@ __global__ void __launch_bounds__(kBlock) context_windows_kernel(const int64_t* 
       }
     }
   }
+}
+
+// Narrow transport of the host entry points: int64 ids that fit 32 bits are packed to int32 before
+// they cross PCIe. Four elements per thread and trip (two 16-byte loads, one 16-byte store); both
+// arrays start on 16-byte boundaries, the tail goes element by element.
+__global__ void __launch_bounds__(kBlock) narrow_i64_kernel(const int64_t* __restrict__ in, int64_t count,
+                                                            int32_t* __restrict__ out) {
+  const int64_t quads = count >> 2;
+  const int64_t stride = (int64_t)gridDim.x * kBlock;
+  for (int64_t i = (int64_t)blockIdx.x * kBlock + threadIdx.x; i < quads; i += stride) {
+    const longlong2 a = __ldcs(reinterpret_cast<const longlong2*>(in) + 2 * i);
+    const longlong2 b = __ldcs(reinterpret_cast<const longlong2*>(in) + 2 * i + 1);
+    reinterpret_cast<int4*>(out)[i] = make_int4((int32_t)a.x, (int32_t)a.y, (int32_t)b.x, (int32_t)b.y);
+  }
+  const int64_t tail = (quads << 2) + (int64_t)blockIdx.x * kBlock + threadIdx.x;
+  if (tail < count) out[tail] = (int32_t)in[tail];
 }
 
 }  // namespace walk_b200

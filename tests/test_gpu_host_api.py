@@ -17,6 +17,9 @@ pytestmark = pytest.mark.gpu
 def _reset():
     yield
     _lib.set_tuning("host_slab_mb", 256)
+    _lib.set_tuning("host_narrow", 1)
+    _lib.set_tuning("host_threads", 0)
+    _lib.set_tuning("host_single_launch", 1)
     clear_caches()
 
 
@@ -57,6 +60,43 @@ def test_slab_pipeline_many_slabs(cuda):
         if slab_mb == 1:
             assert launches >= 8
         out = rejection_sampling(rowptr, col, start, L, 0.25, 4.0, seed=8, walk_index_base=17, symmetric=True)
+        np.testing.assert_array_equal(out.numpy(), want_b)
+
+
+def test_narrow_transport_is_invisible(cuda):
+    """Ids that fit int32 cross the bus as int32 and are widened by host threads, and node2vec runs
+    as one launch whose finished slabs are copied out behind it: the walk and edge matrices must
+    equal the plain int64 slab pipeline's for any slab size, thread count and buffer kind (pinned or
+    pageable), including the -1 edge entries of walks parked on isolated nodes."""
+    from mlx_cluster_b200 import graphs
+    rowptr, col = graphs.rmat_csr(13, 6, seed=5)
+    n_nodes = rowptr.numel() - 1
+    rng = np.random.default_rng(2)
+    walks, L = 70001, 19
+    start_np = rng.integers(0, n_nodes, walks).astype(np.int64)
+    rand_np = rng.random((walks, L), dtype=np.float32)
+    want_n, want_e = oracle.uniform_walk(rowptr.numpy(), col.numpy(), start_np, rand_np, L, return_edges=True)
+    assert (want_e == -1).any()
+    want_b, want_be = oracle.node2vec_walk(rowptr.numpy(), col.numpy(), start_np, L, 0.25, 4.0, seed=3,
+                                           return_edges=True)
+    for narrow, threads, slab_mb, pinned, single in ((0, 0, 2, True, 1), (1, 1, 2, True, 0), (1, 3, 1, False, 1),
+                                                     (1, 0, 256, True, 1), (1, 5, 3, False, 0), (1, 2, 4, True, 1)):
+        _lib.set_tuning("host_narrow", narrow)
+        _lib.set_tuning("host_single_launch", single)
+        _lib.set_tuning("host_threads", threads)
+        _lib.set_tuning("host_slab_mb", slab_mb)
+        start = torch.from_numpy(start_np)
+        rand = torch.from_numpy(rand_np)
+        if pinned:
+            start, rand = start.pin_memory(), rand.pin_memory()
+        out, e = random_walk(rowptr, col, start, rand, L, return_edges=True)
+        np.testing.assert_array_equal(out.numpy(), want_n)
+        np.testing.assert_array_equal(e.numpy(), want_e)
+        for kw in (dict(symmetric=True), dict(symmetric=False), dict(edgeset=True)):
+            out, e = rejection_sampling(rowptr, col, start, L, 0.25, 4.0, seed=3, return_edges=True, **kw)
+            np.testing.assert_array_equal(out.numpy(), want_b)
+            np.testing.assert_array_equal(e.numpy(), want_be)
+        out = rejection_sampling(rowptr, col, start, L, 0.25, 4.0, seed=3, edgeset=True)
         np.testing.assert_array_equal(out.numpy(), want_b)
 
 
