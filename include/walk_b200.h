@@ -222,8 +222,15 @@ int walk_b200_shard_count_cyclic(int64_t num_walks, int32_t world_size, int32_t 
  * For callers whose arrays live in host memory. The graph is uploaded once and stays
  * resident on the device that was current at creation; each walk call then moves
  * only its own batch: start (+ rand) host->device and the walk matrix device->host,
- * in slabs so that copies overlap the kernel. Host buffers should be pinned
- * (cudaHostAlloc / cudaHostRegister) for the copies to overlap.
+ * in slabs so that copies overlap the kernel. start and rand should be pinned
+ * (cudaHostAlloc / cudaHostRegister) for the uploads to overlap.
+ * When every id fits 31 bits the matrices cross the bus as int32 into pinned staging
+ * owned by the graph and host threads of the library widen them into the caller's
+ * int64 buffers (which may then be pageable); node2vec runs as one launch whose
+ * finished slabs are copied out while it goes on, and keeps the int32 matrices in
+ * device memory for the duration of the call. Results are identical either way. A
+ * call returns when the caller's buffers are written; on a non-zero return their
+ * contents are unspecified.
  */
 typedef struct walk_b200_graph walk_b200_graph;
 
