@@ -463,6 +463,8 @@ def run_ours(args, wl):
                     hg._h, h_start.data_ptr(), h_rand.data_ptr(), rows, L, h_out.data_ptr(), None))
 
         narrow = n_nodes < 2 ** 31 and _lib.get_tuning("host_narrow") != 0
+        if world > 1 and _lib.get_tuning("host_threads") == 0:  # the ranks of one box share its cores
+            _lib.set_tuning("host_threads", max(2, min(16, len(os.sched_getaffinity(0)) // world)))
         host_step()
         if barrier:
             barrier()
@@ -474,7 +476,8 @@ def run_ours(args, wl):
         e2e = {"value": walks_timed * L / (e2e_ms * 1e-3), "unit": "steps/s",
                "h2d_bytes_per_step": int(allsum(rows * 8 + (rows * L * 4 if rand is not None else 0))),
                "d2h_bytes_per_step": int(allsum(rows * (L + 1) * (4 if narrow else 8))),
-               "ms_per_step": e2e_ms, "steps": e2e_steps,
+               "ms_per_step": e2e_ms, "steps": e2e_steps, "host_threads_per_rank": _lib.get_tuning("host_threads") or
+               min(16, len(os.sched_getaffinity(0))),
                "transport": "int32 on the bus, widened to the caller's int64 buffer by host threads" if narrow
                else "int64",
                "api": "walk_b200_*_walk_host (C ABI, pinned host buffers, graph resident)",
