@@ -218,6 +218,30 @@ int walk_b200_shard_range(int64_t num_walks, int32_t world_size, int32_t rank,
  * by 25 % in work). */
 int walk_b200_shard_count_cyclic(int64_t num_walks, int32_t world_size, int32_t rank, int64_t* count);
 
+/* ---- edge list -> CSR on the device ----------------------------------------------
+ * The step in front of the walks. The reference's demos sort the edge index on the
+ * host and derive rowptr from the counts of the row ids that occur, which loses
+ * isolated nodes (tests/test_random_walk.py:22-28 of the reference project); here
+ * num_nodes is an argument and rowptr always has num_nodes + 1 entries.
+ * src/dst: int64 [num_input_edges] device arrays. Output: rowptr int64 [num_nodes + 1],
+ * col int64 with room for num_input_edges entries (twice that with
+ * WALK_B200_BUILD_SYMMETRIZE); rows come out sorted ascending; the number of edges
+ * written is rowptr[num_nodes] (read it from the device after the stream has caught
+ * up). Edges with an endpoint outside [0, num_nodes) are left out and raise
+ * WALK_B200_FLAG_BAD_NODE. Needs num_nodes < 2^31 and num_input_edges < 2^31.
+ * scratch: device memory, 256-byte aligned, walk_b200_csr_build_scratch_bytes() bytes,
+ * free again when the stream has passed the call. Nothing is read back to the host.
+ */
+#define WALK_B200_BUILD_SYMMETRIZE 0x1u      /* also insert every edge reversed */
+#define WALK_B200_BUILD_DROP_SELF_LOOPS 0x2u /* leave out u -> u */
+#define WALK_B200_BUILD_DEDUPE 0x4u          /* keep one copy of a repeated edge */
+
+int walk_b200_csr_build_scratch_bytes(int64_t num_input_edges, int64_t num_nodes, uint32_t options,
+                                      uint64_t* bytes);
+int walk_b200_csr_build(const int64_t* src, const int64_t* dst, int64_t num_input_edges,
+                        int64_t num_nodes, uint32_t options, void* scratch, uint64_t scratch_bytes,
+                        int64_t* rowptr, int64_t* col, uint32_t* status_flags, void* stream);
+
 /* ---- resident graph + host-buffer entry points ---------------------------------
  * For callers whose arrays live in host memory. The graph is uploaded once and stays
  * resident on the device that was current at creation; each walk call then moves

@@ -31,7 +31,9 @@ EXPORTS = (
     "walk_b200_l2_window_set", "walk_b200_l2_window_clear",
     "walk_b200_set_tuning", "walk_b200_get_tuning",
     "walk_b200_uniform_walk_noalloc", "walk_b200_gather_probe", "walk_b200_context_windows",
+    "walk_b200_csr_build_scratch_bytes", "walk_b200_csr_build",
 )
+BUILD_SYMMETRIZE, BUILD_DROP_SELF_LOOPS, BUILD_DEDUPE = 0x1, 0x2, 0x4
 NOALLOC_MAX_NODES = 1 << 20
 
 
@@ -94,6 +96,8 @@ def lib():
     L.walk_b200_l2_window_clear.argtypes = [vp]
     L.walk_b200_uniform_walk_noalloc.argtypes = [vp, vp, i64, i64, vp, vp, i64, i32, vp, vp, vp, vp]
     L.walk_b200_context_windows.argtypes = [vp, i64, i32, i32, vp, vp]
+    L.walk_b200_csr_build_scratch_bytes.argtypes = [i64, i64, C.c_uint32, C.POINTER(C.c_uint64)]
+    L.walk_b200_csr_build.argtypes = [vp, vp, i64, i64, C.c_uint32, vp, C.c_uint64, vp, vp, vp, vp]
     L.walk_b200_gather_probe.argtypes = [C.c_size_t, i32, C.POINTER(dbl)]
     L.walk_b200_set_tuning.argtypes = [C.c_char_p, i32]
     L.walk_b200_get_tuning.argtypes = [C.c_char_p, C.POINTER(i32)]

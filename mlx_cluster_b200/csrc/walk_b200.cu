@@ -17,6 +17,7 @@
 #include <thread>
 
 #include "../../include/walk_b200.h"
+#include "host_common.h"
 #include "host_widen.h"
 #include "walk_kernels.cuh"
 
@@ -402,6 +403,26 @@ int grid_for_streaming(int64_t n) {
 }
 
 }  // namespace
+
+namespace walk_b200 {
+namespace host {
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+int check_launch(const char* what) { return ::check_launch(what); }
+
+int sm_count() { return ::sm_count(); }
+
+}  // namespace host
+}  // namespace walk_b200
 
 // ======================================================================================
 // C ABI

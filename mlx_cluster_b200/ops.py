@@ -448,3 +448,42 @@ def context_windows(walks: torch.Tensor, context_size: int, *, stream=None, out:
                 raise ValueError("out has the wrong size")
         _lib.check(_lib.lib().walk_b200_context_windows(_ptr(walks), n, row - 1, cs, _ptr(out), _stream_handle(stream, dev)))
     return out
+
+
+def csr_from_edges(src: torch.Tensor, dst: torch.Tensor, num_nodes: int, *, symmetrize: bool = True,
+                   drop_self_loops: bool = True, dedupe: bool = True, stream=None, check: bool = True):
+    """Edge list -> ``(rowptr, col)`` on the device, rows sorted ascending, ``rowptr`` over all
+    ``num_nodes`` nodes (isolated nodes keep their empty rows -- the host recipe of the reference's
+    demos, ``tests/test_random_walk.py:22-28`` there, loses them).
+
+    ``src``/``dst``: int64 CUDA tensors of equal length. ``symmetrize`` also inserts every edge
+    reversed, ``dedupe`` keeps one copy of a repeated edge. With ``check`` an endpoint outside
+    ``[0, num_nodes)`` raises; without it such edges are silently left out. The call synchronises
+    once, to learn the number of edges and trim ``col``.
+    """
+    _require(src, "src", torch.int64)
+    _require(dst, "dst", torch.int64, src.device if src.is_cuda else None)
+    if not src.is_cuda or src.dim() != 1 or dst.shape != src.shape:
+        raise ValueError("src and dst must be 1-D CUDA tensors of equal length")
+    dev = src.device
+    m, n = src.numel(), int(num_nodes)
+    options = ((_lib.BUILD_SYMMETRIZE if symmetrize else 0) | (_lib.BUILD_DROP_SELF_LOOPS if drop_self_loops else 0) |
+               (_lib.BUILD_DEDUPE if dedupe else 0))
+    with torch.cuda.device(dev):
+        need = C.c_uint64(0)
+        _lib.check(_lib.lib().walk_b200_csr_build_scratch_bytes(m, n, options, C.byref(need)))
+        scratch = torch.empty(max(int(need.value), 256), dtype=torch.uint8, device=dev)
+        rowptr = torch.empty(n + 1, dtype=torch.int64, device=dev)
+        col = torch.empty(max(1, m * (2 if symmetrize else 1)), dtype=torch.int64, device=dev)
+        flags = torch.zeros(1, dtype=torch.int32, device=dev)
+        src, dst = src.contiguous(), dst.contiguous()
+        _lib.check(_lib.lib().walk_b200_csr_build(_ptr(src), _ptr(dst), m, n, options, _ptr(scratch), int(need.value),
+                                                  _ptr(rowptr), _ptr(col), _ptr(flags), _stream_handle(stream, dev)))
+        if isinstance(stream, torch.cuda.Stream):
+            stream.synchronize()
+        elif stream is not None:
+            torch.cuda.synchronize(dev)
+        nnz = int(rowptr[-1].item())
+        if check and int(flags.item()) & _lib.FLAG_BAD_NODE:
+            raise _lib.WalkError(_lib.ERR_DEVICE_FLAGS, "edge list holds a node id outside [0, num_nodes)")
+    return rowptr, col[:nnz]
