@@ -30,6 +30,7 @@ namespace {
 constexpr int kBuildBlock = 256;
 constexpr int kBuildWarps = kBuildBlock / 32;
 constexpr uint32_t kSmallRow = 64;         // rows up to this many raw entries: one warp, registers
+constexpr uint32_t kSharedRow = 4096;      // longer rows up to this: block radix sort inside shared memory
 constexpr uint32_t kPadKey = 0xffffffffu;  // sorts behind every node id (ids are below 2^31)
 constexpr unsigned kFullMask = 0xffffffffu;
 constexpr int kScanItems = 16;             // items per thread of one scan tile
@@ -40,14 +41,15 @@ __device__ __forceinline__ void raise(uint32_t* flags, uint32_t bit) {
 }
 
 // ---- 1. count / 3. fill ------------------------------------------------------------------------
-// FILL = false: count the entries of every row. FILL = true: place them (the counters count down
-// to zero again, so afterwards they are free for the per-row results of the sort).
+// FILL = false: count the entries of every row. FILL = true: place them; by then the scan has
+// turned each counter into its row's end offset (32 bits are enough: there are fewer than 2^32
+// slots), so one atomicSub both claims a slot and says where it is. Afterwards the counters are
+// free for the per-row results of the sort.
 template <bool FILL>
 __global__ void __launch_bounds__(kBuildBlock) csr_edges_kernel(const int64_t* __restrict__ src,
                                                                 const int64_t* __restrict__ dst, int64_t m,
                                                                 int64_t num_nodes, uint32_t options,
                                                                 uint32_t* __restrict__ counters,
-                                                                const int64_t* __restrict__ raw_rowptr,
                                                                 uint32_t* __restrict__ raw_col,
                                                                 uint32_t* __restrict__ flags) {
   const bool sym = (options & WALK_B200_BUILD_SYMMETRIZE) != 0;
@@ -64,8 +66,8 @@ __global__ void __launch_bounds__(kBuildBlock) csr_edges_kernel(const int64_t* _
       atomicAdd(counters + u, 1u);
       if (sym && u != v) atomicAdd(counters + v, 1u);
     } else {
-      raw_col[raw_rowptr[u] + (int64_t)(atomicSub(counters + u, 1u) - 1u)] = (uint32_t)v;
-      if (sym && u != v) raw_col[raw_rowptr[v] + (int64_t)(atomicSub(counters + v, 1u) - 1u)] = (uint32_t)u;
+      raw_col[atomicSub(counters + u, 1u) - 1u] = (uint32_t)v;
+      if (sym && u != v) raw_col[atomicSub(counters + v, 1u) - 1u] = (uint32_t)u;
     }
   }
 }
@@ -122,7 +124,9 @@ __global__ void __launch_bounds__(kBuildBlock) scan_tile_offsets_kernel(uint64_t
   }
 }
 
-__global__ void __launch_bounds__(kBuildBlock) scan_write_kernel(const uint32_t* __restrict__ in, int64_t n,
+// ENDS: the count of row i is replaced by the low 32 bits of the row's end offset (the fill's cursor).
+template <bool ENDS>
+__global__ void __launch_bounds__(kBuildBlock) scan_write_kernel(uint32_t* __restrict__ in, int64_t n,
                                                                  const uint64_t* __restrict__ tile_offsets,
                                                                  int64_t* __restrict__ out /* [n + 1] */) {
   __shared__ uint64_t warp_sums[kBuildWarps];
@@ -135,6 +139,7 @@ __global__ void __launch_bounds__(kBuildBlock) scan_write_kernel(const uint32_t*
     uint64_t total;
     const uint64_t ex = block_exclusive_scan(x, &total, warp_sums);
     if (i < n) out[i] = (int64_t)(carry + ex);
+    if (ENDS && i < n) in[i] = (uint32_t)(carry + ex + x);
     if (i == n - 1) out[n] = (int64_t)(carry + ex + x);
     carry += total;
   }
@@ -213,6 +218,7 @@ __global__ void __launch_bounds__(kBuildBlock) csr_sort_long_kernel(const int64_
                                                                     const uint32_t* __restrict__ long_rows,
                                                                     const unsigned long long* __restrict__ long_count) {
   __shared__ uint32_t offs[kBuildWarps][256];
+  __shared__ uint32_t stage[2][kSharedRow];  // rows that fit are sorted here instead of in global memory
   __shared__ uint64_t warp_sums[kBuildWarps];
   __shared__ uint32_t tile_warp_kept[kBuildWarps];
   const bool dedupe = (options & WALK_B200_BUILD_DEDUPE) != 0;
@@ -229,6 +235,12 @@ __global__ void __launch_bounds__(kBuildBlock) csr_sort_long_kernel(const int64_
     const uint32_t p_end = (uint32_t)min((uint64_t)d, piece * (uint64_t)(warp + 1));
     uint32_t* cur = raw_col + s;
     uint32_t* alt = tmp + s;
+    if (d <= kSharedRow) {
+      for (uint32_t i = threadIdx.x; i < d; i += kBuildBlock) stage[0][i] = cur[i];
+      cur = stage[0];
+      alt = stage[1];
+      __syncthreads();
+    }
     for (int32_t pass = 0; pass < passes; pass++) {
       const int shift = pass * digit_bits;
       for (int k = threadIdx.x; k < kBuildWarps * 256; k += kBuildBlock) (&offs[0][0])[k] = 0;
@@ -368,7 +380,7 @@ int check_build_args(int64_t m, int64_t num_nodes, uint32_t options) {
   return WALK_B200_OK;
 }
 
-int scan_counts(const uint32_t* counts, int64_t n, uint64_t* tile_sums, int64_t* out, cudaStream_t s) {
+int scan_counts(uint32_t* counts, int64_t n, uint64_t* tile_sums, int64_t* out, bool ends, cudaStream_t s) {
   if (n == 0) {
     WALK_CUDA_TRY(cudaMemsetAsync(out, 0, 8, s));
     return WALK_B200_OK;
@@ -378,7 +390,8 @@ int scan_counts(const uint32_t* counts, int64_t n, uint64_t* tile_sums, int64_t*
   if (int rc = host::check_launch("scan_tile_sums_kernel")) return rc;
   scan_tile_offsets_kernel<<<1, kBuildBlock, 0, s>>>(tile_sums, tiles);
   if (int rc = host::check_launch("scan_tile_offsets_kernel")) return rc;
-  scan_write_kernel<<<(unsigned)tiles, kBuildBlock, 0, s>>>(counts, n, tile_sums, out);
+  if (ends) scan_write_kernel<true><<<(unsigned)tiles, kBuildBlock, 0, s>>>(counts, n, tile_sums, out);
+  else scan_write_kernel<false><<<(unsigned)tiles, kBuildBlock, 0, s>>>(counts, n, tile_sums, out);
   return host::check_launch("scan_write_kernel");
 }
 
@@ -435,11 +448,11 @@ int walk_b200_csr_build(const int64_t* src, const int64_t* dst, int64_t num_inpu
 
   const unsigned edge_grid = capped_grid((num_input_edges + kBuildBlock - 1) / kBuildBlock, 16);
   csr_edges_kernel<false><<<edge_grid, kBuildBlock, 0, s>>>(src, dst, num_input_edges, num_nodes, options, counters,
-                                                            nullptr, nullptr, status_flags);
+                                                            nullptr, status_flags);
   if (int rc = host::check_launch("csr_edges_kernel<count>")) return rc;
-  if (int rc = scan_counts(counters, num_nodes, tile_sums, raw_rowptr, s)) return rc;
+  if (int rc = scan_counts(counters, num_nodes, tile_sums, raw_rowptr, true, s)) return rc;
   csr_edges_kernel<true><<<edge_grid, kBuildBlock, 0, s>>>(src, dst, num_input_edges, num_nodes, options, counters,
-                                                           raw_rowptr, raw_col, status_flags);
+                                                           raw_col, status_flags);
   if (int rc = host::check_launch("csr_edges_kernel<fill>")) return rc;
 
   const unsigned row_grid = capped_grid((num_nodes + kBuildWarps - 1) / kBuildWarps, 16);
@@ -455,7 +468,7 @@ int walk_b200_csr_build(const int64_t* src, const int64_t* dst, int64_t num_inpu
                                                          long_rows, long_count);
   if (int rc = host::check_launch("csr_sort_long_kernel")) return rc;
 
-  if (int rc = scan_counts(counters, num_nodes, tile_sums, rowptr, s)) return rc;
+  if (int rc = scan_counts(counters, num_nodes, tile_sums, rowptr, false, s)) return rc;
   csr_emit_small_kernel<<<row_grid, kBuildBlock, 0, s>>>(raw_rowptr, raw_col, rowptr, num_nodes, col);
   if (int rc = host::check_launch("csr_emit_small_kernel")) return rc;
   csr_emit_long_kernel<<<long_grid, kBuildBlock, 0, s>>>(raw_rowptr, raw_col, rowptr, long_rows, long_count, col);
