@@ -331,6 +331,20 @@ int walk_b200_context_windows(const int64_t* walks, int64_t num_walks, int32_t w
                               int32_t context_size, int64_t* windows, void* stream);
 
 /*
+ * Negative samples of the skip-gram loss, shaped like walks so that walk_b200_context_windows applies
+ * to them unchanged (no counterpart in the reference): out[r, 0] = start[r], out[r, 1 + k] = a node id
+ * drawn uniformly from [0, num_nodes), k < walk_length. out is int64 [num_rows, walk_length + 1], device.
+ * Draw k of global row g = row_index_base + r * row_index_stride (stride 0 means 1) is word (k & 3) of
+ * Philox4x32-10 with key = seed and counter = (g low 32, k >> 2, 0x4E454753, g high 32);
+ * node = (word * num_nodes) >> 32. Needs 1 <= num_nodes <= 2^32. walk_b200_negative_draw replays one
+ * draw on the host.
+ */
+int walk_b200_negative_walks(const int64_t* start, int64_t num_rows, int32_t walk_length,
+                             int64_t num_nodes, uint64_t seed, uint64_t row_index_base,
+                             uint64_t row_index_stride, int64_t* out, void* stream);
+int walk_b200_negative_draw(uint64_t seed, uint64_t row, uint32_t k, int64_t num_nodes, int64_t* node);
+
+/*
  * Device probe (diagnostic; allocates and frees array_bytes of device memory itself):
  * the rate of dependent random 8-byte gathers over an array much larger than L2, one
  * gather in flight per thread -- the access pattern of a walk step. On B200 this rate,

@@ -32,6 +32,7 @@ EXPORTS = (
     "walk_b200_set_tuning", "walk_b200_get_tuning",
     "walk_b200_uniform_walk_noalloc", "walk_b200_gather_probe", "walk_b200_context_windows",
     "walk_b200_csr_build_scratch_bytes", "walk_b200_csr_build",
+    "walk_b200_negative_walks", "walk_b200_negative_draw",
 )
 BUILD_SYMMETRIZE, BUILD_DROP_SELF_LOOPS, BUILD_DEDUPE = 0x1, 0x2, 0x4
 NOALLOC_MAX_NODES = 1 << 20
@@ -96,6 +97,8 @@ def lib():
     L.walk_b200_l2_window_clear.argtypes = [vp]
     L.walk_b200_uniform_walk_noalloc.argtypes = [vp, vp, i64, i64, vp, vp, i64, i32, vp, vp, vp, vp]
     L.walk_b200_context_windows.argtypes = [vp, i64, i32, i32, vp, vp]
+    L.walk_b200_negative_walks.argtypes = [vp, i64, i32, i64, C.c_uint64, C.c_uint64, C.c_uint64, vp, vp]
+    L.walk_b200_negative_draw.argtypes = [C.c_uint64, C.c_uint64, C.c_uint32, i64, C.POINTER(i64)]
     L.walk_b200_csr_build_scratch_bytes.argtypes = [i64, i64, C.c_uint32, C.POINTER(C.c_uint64)]
     L.walk_b200_csr_build.argtypes = [vp, vp, i64, i64, C.c_uint32, vp, C.c_uint64, vp, vp, vp, vp]
     L.walk_b200_gather_probe.argtypes = [C.c_size_t, i32, C.POINTER(dbl)]
@@ -179,3 +182,10 @@ def shard_range(num_walks: int, world_size: int, rank: int):
     b, e = C.c_int64(0), C.c_int64(0)
     check(lib().walk_b200_shard_range(num_walks, world_size, rank, C.byref(b), C.byref(e)))
     return int(b.value), int(e.value)
+
+
+def negative_draw(seed: int, row: int, k: int, num_nodes: int) -> int:
+    """Host replay of draw ``k`` of global row ``row`` of ``walk_b200_negative_walks``."""
+    v = C.c_int64(0)
+    check(lib().walk_b200_negative_draw(seed, row, k, num_nodes, C.byref(v)))
+    return int(v.value)

@@ -55,4 +55,16 @@ __host__ __device__ __forceinline__ float uniform_from_word(uint32_t w) {
   return (float)(w >> 8) * (1.0f / 16777216.0f);
 }
 
+// Negative samples of the skip-gram loss: draw k of row g is word (k & 3) of the block with
+// counter = (g lo32, k >> 2, kNegativeTag, g hi32); node = (word * num_nodes) >> 32.
+constexpr uint32_t kNegativeTag = 0x4E454753u;
+
+__host__ __device__ __forceinline__ Philox4 negative_block(uint32_t k0, uint32_t k1, uint64_t row, uint32_t quad) {
+  return philox4x32_10((uint32_t)row, quad, kNegativeTag, (uint32_t)(row >> 32), k0, k1);
+}
+
+__host__ __device__ __forceinline__ int64_t negative_from_word(uint32_t w, uint64_t num_nodes) {
+  return (int64_t)(((uint64_t)w * num_nodes) >> 32);
+}
+
 }  // namespace walk_b200

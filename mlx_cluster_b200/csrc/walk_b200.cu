@@ -678,6 +678,34 @@ int walk_b200_context_windows(const int64_t* walks, int64_t num_walks, int32_t w
   return check_launch("context_windows_kernel");
 }
 
+int walk_b200_negative_walks(const int64_t* start, int64_t num_rows, int32_t walk_length, int64_t num_nodes,
+                             uint64_t seed, uint64_t row_index_base, uint64_t row_index_stride, int64_t* out,
+                             void* stream) {
+  if (num_rows < 0 || walk_length < 0) return fail(WALK_B200_ERR_INVALID_ARG, "negative size");
+  if (num_nodes < 1 || num_nodes > (1ll << 32))
+    return fail(WALK_B200_ERR_UNSUPPORTED, "negative sampling draws from [0, num_nodes) with 1 <= num_nodes <= 2^32");
+  if (num_rows == 0) return WALK_B200_OK;
+  if (!start || !out) return fail(WALK_B200_ERR_INVALID_ARG, "start or out is NULL");
+  const uint32_t quads = walk_length > 0 ? (uint32_t)((walk_length + 3) / 4) : 1u;
+  if (num_rows > INT64_MAX / 8 / ((int64_t)walk_length + 1)) return fail(WALK_B200_ERR_INVALID_ARG, "matrix too large");
+  int64_t blocks = blocks_for(num_rows * (int64_t)quads);
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  negative_walks_kernel<<<(unsigned)blocks, kBlock, 0, (cudaStream_t)stream>>>(
+      start, num_rows, walk_length, quads, (uint64_t)num_nodes, (uint32_t)seed, (uint32_t)(seed >> 32), row_index_base,
+      row_index_stride ? row_index_stride : 1, out);
+  return check_launch("negative_walks_kernel");
+}
+
+int walk_b200_negative_draw(uint64_t seed, uint64_t row, uint32_t k, int64_t num_nodes, int64_t* node) {
+  if (!node) return fail(WALK_B200_ERR_INVALID_ARG, "node is NULL");
+  if (num_nodes < 1 || num_nodes > (1ll << 32)) return fail(WALK_B200_ERR_UNSUPPORTED, "num_nodes must be in [1, 2^32]");
+  const Philox4 b = negative_block((uint32_t)seed, (uint32_t)(seed >> 32), row, k >> 2);
+  const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+  *node = negative_from_word(w[k & 3], (uint64_t)num_nodes);
+  return WALK_B200_OK;
+}
+
 // ---- device probe -------------------------------------------------------------------
 int walk_b200_gather_probe(size_t array_bytes, int32_t iters, double* gathers_per_second) {
   if (!gathers_per_second || iters < 1 || array_bytes < (1u << 20))

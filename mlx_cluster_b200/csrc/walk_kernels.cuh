@@ -972,6 +972,32 @@ __global__ void __launch_bounds__(kBlock) context_windows_kernel(const int64_t* 
   }
 }
 
+// Negative rows for the skip-gram loss: out[r, 0] = start[r], out[r, 1 + k] = a node drawn uniformly
+// from [0, num_nodes). One thread per Philox block = four consecutive draws of one row; consecutive
+// threads write consecutive 32-byte pieces of a row.
+__global__ void __launch_bounds__(kBlock) negative_walks_kernel(const int64_t* __restrict__ start, int64_t num_rows,
+                                                                int32_t L, uint32_t quads_per_row, uint64_t num_nodes,
+                                                                uint32_t key0, uint32_t key1, uint64_t row_base,
+                                                                uint64_t row_stride, int64_t* __restrict__ out) {
+  const L2Policy pol = make_policies(2);
+  const int64_t total = num_rows * (int64_t)quads_per_row;
+  const int64_t stride = (int64_t)gridDim.x * kBlock;
+  for (int64_t t = (int64_t)blockIdx.x * kBlock + threadIdx.x; t < total; t += stride) {
+    const int64_t r = t / quads_per_row;
+    const uint32_t quad = (uint32_t)(t - r * quads_per_row);
+    int64_t* row = out + r * ((int64_t)L + 1);
+    if (quad == 0) st8(row, __ldg(start + r), pol.stream);
+    if (L == 0) continue;
+    const Philox4 b = negative_block(key0, key1, row_base + (uint64_t)r * row_stride, quad);
+    const uint32_t w[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+      const int32_t draw = (int32_t)(quad * 4u) + k;
+      if (draw < L) st8(row + 1 + draw, negative_from_word(w[k], num_nodes), pol.stream);
+    }
+  }
+}
+
 // Narrow transport of the host entry points: int64 ids that fit 32 bits are packed to int32 before
 // they cross PCIe. Four elements per thread and trip (two 16-byte loads, one 16-byte store); both
 // arrays start on 16-byte boundaries, the tail goes element by element.

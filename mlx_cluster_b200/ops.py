@@ -487,3 +487,27 @@ def csr_from_edges(src: torch.Tensor, dst: torch.Tensor, num_nodes: int, *, symm
         if check and int(flags.item()) & _lib.FLAG_BAD_NODE:
             raise _lib.WalkError(_lib.ERR_DEVICE_FLAGS, "edge list holds a node id outside [0, num_nodes)")
     return rowptr, col[:nnz]
+
+
+def negative_walks(start: torch.Tensor, walk_length: int, num_nodes: int, *, seed: int = 0, row_index_base: int = 0,
+                   row_index_stride: int = 1, stream=None, out: Optional[torch.Tensor] = None):
+    """Negative samples shaped like walks: int64 ``[n, walk_length + 1]`` with column 0 = ``start`` and
+    the other columns node ids drawn uniformly from ``[0, num_nodes)`` (Philox4x32-10, key = ``seed``,
+    indexed by global row and column, so shards of the rows reproduce the unsharded result). Feed it to
+    :func:`context_windows` like a walk matrix to get the negative pairs of the skip-gram loss."""
+    _require(start, "start", torch.int64)
+    if not start.is_cuda or start.dim() != 1:
+        raise ValueError("start must be a 1-D CUDA tensor")
+    n, L = start.numel(), int(walk_length)
+    dev = start.device
+    with torch.cuda.device(dev):
+        if out is None:
+            out = torch.empty((n, L + 1), dtype=torch.int64, device=dev)
+        else:
+            _require(out, "out", torch.int64, dev)
+            if out.numel() != n * (L + 1) or not out.is_contiguous():
+                raise ValueError("out has the wrong size or is not contiguous")
+        _lib.check(_lib.lib().walk_b200_negative_walks(_ptr(start.contiguous()), n, L, int(num_nodes), int(seed),
+                                                       int(row_index_base), int(row_index_stride), _ptr(out),
+                                                       _stream_handle(stream, dev)))
+    return out

@@ -53,6 +53,23 @@ def test_host_philox_matches_independent_implementation_and_oracle(walklib):
         assert _lib.node2vec_draw(seed, walk, step, attempt) == (int(o[0]) >> 1, int(o[1]) >> 1)
 
 
+def test_negative_draw_replays_the_documented_stream(walklib):
+    """Draw k of row g: word (k & 3) of the Philox block (g lo, k >> 2, 'NEGS', g hi), scaled to [0, N)."""
+    rng = np.random.default_rng(11)
+    for _ in range(200):
+        seed = int(rng.integers(0, 2**63)) * 2 + int(rng.integers(0, 2))
+        row = int(rng.integers(0, 2**40))
+        k = int(rng.integers(0, 500))
+        n = int(rng.integers(1, 2**32 + 1))
+        o = oracle.philox4x32_10([row & 0xffffffff, k >> 2, 0x4E454753, row >> 32], [seed & 0xffffffff, seed >> 32])
+        got = _lib.negative_draw(seed, row, k, n)
+        assert got == (int(o[k & 3]) * n) >> 32 and 0 <= got < n
+    with pytest.raises(_lib.WalkError):
+        _lib.negative_draw(1, 2, 3, 0)
+    with pytest.raises(_lib.WalkError):
+        _lib.negative_draw(1, 2, 3, 2**32 + 1)
+
+
 def test_thresholds_and_cuts_match_oracle(walklib):
     for p, q in [(1, 1), (0.5, 2), (4, 0.25), (0.25, 4), (1, 2), (1, 3), (0.7, 1.3), (3.3, 0.011), (100.0, 100.0)]:
         prob, cuts = _lib.node2vec_thresholds(p, q)

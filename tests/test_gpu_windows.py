@@ -32,3 +32,50 @@ def test_windows_argument_errors(cuda):
     with pytest.raises(TypeError):
         context_windows(walks.int(), 3)
     assert _lib.lib().walk_b200_context_windows(walks.data_ptr(), 4, 5, 9, walks.data_ptr(), None) == _lib.ERR_INVALID_ARG
+
+
+@pytest.mark.parametrize("n,L,num_nodes", [(1, 1, 7), (33, 5, 1000), (257, 20, 1 << 24), (1000, 0, 5), (64, 7, 1 << 32)])
+def test_negative_walks_match_host_replay(cuda, n, L, num_nodes):
+    """Column 0 is the start node, the rest the documented Philox draws (replayed on the host through
+    walk_b200_negative_draw, itself checked against an independent Philox in the CPU suite)."""
+    from mlx_cluster_b200 import _lib, negative_walks
+    rng = np.random.default_rng(n + L)
+    start = torch.from_numpy(rng.integers(0, min(num_nodes, 2**62), n).astype(np.int64)).cuda()
+    seed, base, stride = 0xfeedbeef12345678, 2**33 + 3, 5
+    out = negative_walks(start, L, num_nodes, seed=seed, row_index_base=base, row_index_stride=stride).cpu().numpy()
+    assert out.shape == (n, L + 1)
+    np.testing.assert_array_equal(out[:, 0], start.cpu().numpy())
+    rows = sorted(set([0, n - 1, n // 2] + list(rng.integers(0, n, 8))))
+    for r in rows:
+        want = [_lib.negative_draw(seed, base + int(r) * stride, k, num_nodes) for k in range(L)]
+        assert out[r, 1:].tolist() == want
+    if L:
+        assert out[:, 1:].min() >= 0 and out[:, 1:].max() < num_nodes
+
+
+def test_negative_walks_shards_and_spread(cuda):
+    """Rows dealt cyclically to two 'ranks' reproduce the unsharded matrix, and the draws cover the
+    node range evenly (chi-square over 64 bins at p > 1e-6)."""
+    from scipy import stats
+    from mlx_cluster_b200 import negative_walks
+    n, L, num_nodes = 4096, 40, 100000
+    start = torch.arange(n, dtype=torch.int64, device="cuda")
+    full = negative_walks(start, L, num_nodes, seed=9)
+    for r in range(2):
+        part = negative_walks(start[r::2].contiguous(), L, num_nodes, seed=9, row_index_base=r, row_index_stride=2)
+        assert torch.equal(part, full[r::2])
+    draws = full[:, 1:].reshape(-1).cpu().numpy()
+    counts = np.bincount(draws * 64 // num_nodes, minlength=64).astype(np.float64)
+    expect = np.bincount(np.arange(num_nodes) * 64 // num_nodes, minlength=64) * (draws.size / num_nodes)
+    chi2 = float(((counts - expect) ** 2 / expect).sum())
+    assert float(stats.chi2.sf(chi2, 63)) > 1e-6
+
+
+def test_negative_windows_pipeline(cuda):
+    """Negative rows go through the same window kernel as walks."""
+    from mlx_cluster_b200 import negative_walks
+    start = torch.arange(100, dtype=torch.int64, device="cuda")
+    neg = negative_walks(start, 12, 5000, seed=1)
+    win = context_windows(neg, 5)
+    want = neg.unfold(1, 5, 1).reshape(-1, 5)
+    assert torch.equal(win, want)
