@@ -130,12 +130,16 @@ class ClockSampler:
 
 # ------------------------------------------------------------------------------ graph
 def build_graph(wl, device, world, rank):
-    """Rank 0 builds the seeded R-MAT CSR on its GPU; other ranks receive a replica."""
-    from mlx_cluster_b200 import graphs
+    """Rank 0 draws the seeded R-MAT edge list on its GPU and builds the CSR with the library's
+    device builder (symmetrised, loop-free, duplicate-free); other ranks receive a replica."""
+    from mlx_cluster_b200 import csr_from_edges, graphs
     import torch.distributed as dist
     t0 = time.time()
     if rank == 0:
-        rowptr, col = graphs.rmat_csr(wl["scale"], wl["edge_factor"], seed=wl["seed"], device=device, **RMAT)
+        src, dst = graphs.rmat_edges(wl["scale"], wl["edge_factor"], seed=wl["seed"], device=device, **RMAT)
+        rowptr, col = csr_from_edges(src, dst, 1 << wl["scale"])
+        col = col.clone()  # drop the builder's spare capacity
+        del src, dst
         torch.cuda.synchronize(device)
     if world > 1:
         meta = torch.tensor([rowptr.numel(), col.numel()] if rank == 0 else [0, 0], dtype=torch.int64, device=device)

@@ -30,7 +30,7 @@ namespace {
 constexpr int kBuildBlock = 256;
 constexpr int kBuildWarps = kBuildBlock / 32;
 constexpr uint32_t kSmallRow = 64;         // rows up to this many raw entries: one warp, registers
-constexpr uint32_t kSharedRow = 4096;      // longer rows up to this: block radix sort inside shared memory
+constexpr uint32_t kMediumRow = 2048;      // rows up to this many: one warp, radix sort; longer: one block
 constexpr uint32_t kPadKey = 0xffffffffu;  // sorts behind every node id (ids are below 2^31)
 constexpr unsigned kFullMask = 0xffffffffu;
 constexpr int kScanItems = 16;             // items per thread of one scan tile
@@ -154,8 +154,9 @@ __global__ void __launch_bounds__(kBuildBlock) csr_sort_small_kernel(const int64
                                                                      int64_t num_nodes, uint32_t options,
                                                                      uint32_t* __restrict__ raw_col,
                                                                      uint32_t* __restrict__ kept,
+                                                                     uint32_t* __restrict__ medium_rows,
                                                                      uint32_t* __restrict__ long_rows,
-                                                                     unsigned long long* __restrict__ long_count) {
+                                                                     unsigned long long* __restrict__ list_counts) {
   const bool dedupe = (options & WALK_B200_BUILD_DEDUPE) != 0;
   const int lane = threadIdx.x & 31;
   const int64_t warps = (int64_t)gridDim.x * kBuildWarps;
@@ -166,8 +167,11 @@ __global__ void __launch_bounds__(kBuildBlock) csr_sort_small_kernel(const int64
       if (lane == 0) kept[r] = 0;
       continue;
     }
-    if (d > kSmallRow) {
-      if (lane == 0) long_rows[atomicAdd(long_count, 1ull)] = (uint32_t)r;
+    if (d > kSmallRow) {  // not this kernel's: append to the list of the kernel that sorts it
+      if (lane == 0) {
+        if (d <= kMediumRow) medium_rows[atomicAdd(list_counts + 0, 1ull)] = (uint32_t)r;
+        else long_rows[atomicAdd(list_counts + 1, 1ull)] = (uint32_t)r;
+      }
       continue;
     }
     uint32_t a = (uint32_t)lane < d ? raw_col[s + lane] : kPadKey;
@@ -204,7 +208,94 @@ __global__ void __launch_bounds__(kBuildBlock) csr_sort_small_kernel(const int64
   }
 }
 
-// ---- 4b. longer rows: one block, LSD radix sort between the row and its twin in `tmp` -------------
+// ---- 4b. rows of 65 .. kMediumRow entries: one warp, LSD radix sort between the row and its twin ----
+// Same passes as the block kernel below with a team of one warp: no block barrier anywhere, a
+// 256-bin histogram per warp, lane l owns bins 8l .. 8l+7 in the scan.
+__global__ void __launch_bounds__(kBuildBlock) csr_sort_medium_kernel(const int64_t* __restrict__ raw_rowptr,
+                                                                      uint32_t options, int32_t passes, int32_t digit_bits,
+                                                                      uint32_t* __restrict__ raw_col,
+                                                                      uint32_t* __restrict__ tmp,
+                                                                      uint32_t* __restrict__ kept,
+                                                                      const uint32_t* __restrict__ medium_rows,
+                                                                      const unsigned long long* __restrict__ medium_count) {
+  __shared__ uint32_t hist[kBuildWarps][256];
+  const bool dedupe = (options & WALK_B200_BUILD_DEDUPE) != 0;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned lt = (1u << lane) - 1u;
+  const uint32_t digit_mask = (1u << digit_bits) - 1u;
+  uint32_t* bins = hist[warp];
+  const unsigned long long rows = *medium_count;
+  const unsigned long long warps = (unsigned long long)gridDim.x * kBuildWarps;
+  for (unsigned long long w = (unsigned long long)blockIdx.x * kBuildWarps + warp; w < rows; w += warps) {
+    const uint32_t r = medium_rows[w];
+    const int64_t s = raw_rowptr[r];
+    const uint32_t d = (uint32_t)(raw_rowptr[r + 1] - s);
+    uint32_t* cur = raw_col + s;
+    uint32_t* alt = tmp + s;
+    for (int32_t pass = 0; pass < passes; pass++) {
+      const int shift = pass * digit_bits;
+#pragma unroll
+      for (int k = 0; k < 8; k++) bins[lane + 32 * k] = 0;
+      __syncwarp();
+      for (uint32_t i = lane; i < d; i += 32) atomicAdd(&bins[(cur[i] >> shift) & digit_mask], 1u);
+      __syncwarp();
+      {  // exclusive scan of the 256 bins
+        uint32_t c[8], sum = 0;
+#pragma unroll
+        for (int k = 0; k < 8; k++) { c[k] = bins[lane * 8 + k]; sum += c[k]; }
+        uint32_t inc = sum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const uint32_t y = __shfl_up_sync(kFullMask, inc, o);
+          if (lane >= o) inc += y;
+        }
+        uint32_t run = inc - sum;
+#pragma unroll
+        for (int k = 0; k < 8; k++) { bins[lane * 8 + k] = run; run += c[k]; }
+      }
+      __syncwarp();
+      uint32_t v_next = lane < d ? cur[lane] : 0u;
+      for (uint32_t i0 = 0; i0 < d; i0 += 32) {
+        const uint32_t i = i0 + lane;
+        const bool valid = i < d;
+        const uint32_t v = v_next;
+        if (i + 32 < d) v_next = cur[i + 32];
+        const uint32_t digit = valid ? ((v >> shift) & digit_mask) : 0xffffffffu;
+        const unsigned same = __match_any_sync(kFullMask, digit);
+        const uint32_t rank = (uint32_t)__popc(same & lt);
+        uint32_t base = 0;
+        if (valid) base = bins[digit];
+        __syncwarp();
+        if (valid) {
+          alt[base + rank] = v;
+          if (rank == 0) bins[digit] = base + (uint32_t)__popc(same);
+        }
+        __syncwarp();
+      }
+      uint32_t* t = cur; cur = alt; alt = t;
+    }
+    // drop duplicates, compact to the front of the row in raw_col (in place when cur is the row:
+    // a survivor never moves up, and a step's reads come before its writes)
+    uint32_t* out = raw_col + s;
+    uint32_t written = 0;
+    for (uint32_t i0 = 0; i0 < d; i0 += 32) {
+      const uint32_t i = i0 + lane;
+      uint32_t v = 0;
+      bool keep = false;
+      if (i < d) {
+        v = cur[i];
+        keep = !dedupe || i == 0 || cur[i - 1] != v;
+      }
+      const unsigned m = __ballot_sync(kFullMask, keep);
+      if (keep) out[written + (uint32_t)__popc(m & lt)] = v;
+      written += (uint32_t)__popc(m);
+      __syncwarp();
+    }
+    if (lane == 0) kept[r] = written;
+  }
+}
+
+// ---- 4c. longer rows: one block, LSD radix sort between the row and its twin in `tmp` -------------
 // Warp w owns the contiguous piece [w * piece, (w + 1) * piece) of the row. A pass counts digits per
 // warp, turns the counts into one start offset per (digit, warp) -- all of digit k before digit k+1,
 // within a digit warp 0's entries before warp 1's -- and then every warp scatters its piece in order,
@@ -218,7 +309,6 @@ __global__ void __launch_bounds__(kBuildBlock) csr_sort_long_kernel(const int64_
                                                                     const uint32_t* __restrict__ long_rows,
                                                                     const unsigned long long* __restrict__ long_count) {
   __shared__ uint32_t offs[kBuildWarps][256];
-  __shared__ uint32_t stage[2][kSharedRow];  // rows that fit are sorted here instead of in global memory
   __shared__ uint64_t warp_sums[kBuildWarps];
   __shared__ uint32_t tile_warp_kept[kBuildWarps];
   const bool dedupe = (options & WALK_B200_BUILD_DEDUPE) != 0;
@@ -235,12 +325,6 @@ __global__ void __launch_bounds__(kBuildBlock) csr_sort_long_kernel(const int64_
     const uint32_t p_end = (uint32_t)min((uint64_t)d, piece * (uint64_t)(warp + 1));
     uint32_t* cur = raw_col + s;
     uint32_t* alt = tmp + s;
-    if (d <= kSharedRow) {
-      for (uint32_t i = threadIdx.x; i < d; i += kBuildBlock) stage[0][i] = cur[i];
-      cur = stage[0];
-      alt = stage[1];
-      __syncthreads();
-    }
     for (int32_t pass = 0; pass < passes; pass++) {
       const int shift = pass * digit_bits;
       for (int k = threadIdx.x; k < kBuildWarps * 256; k += kBuildBlock) (&offs[0][0])[k] = 0;
@@ -324,7 +408,7 @@ __global__ void __launch_bounds__(kBuildBlock) csr_emit_small_kernel(const int64
   const int64_t warps = (int64_t)gridDim.x * kBuildWarps;
   for (int64_t r = (int64_t)blockIdx.x * kBuildWarps + (threadIdx.x >> 5); r < num_nodes; r += warps) {
     const int64_t s = raw_rowptr[r];
-    if ((uint64_t)(raw_rowptr[r + 1] - s) > kSmallRow) continue;  // a long row: the block kernel's
+    if ((uint64_t)(raw_rowptr[r + 1] - s) > kMediumRow) continue;  // a long row: the block kernel's
     const int64_t o = rowptr[r];
     const int64_t k = rowptr[r + 1] - o;
     for (int64_t j = lane; j < k; j += 32) col[o + j] = (int64_t)raw_col[s + j];
@@ -348,7 +432,7 @@ __global__ void __launch_bounds__(kBuildBlock) csr_emit_long_kernel(const int64_
 
 // ---- scratch layout ----------------------------------------------------------------------------------
 struct BuildLayout {
-  size_t counters, raw_rowptr, tile_sums, raw_col, tmp, long_rows, long_count, total;
+  size_t counters, raw_rowptr, tile_sums, raw_col, tmp, medium_rows, long_rows, list_counts, total;
 };
 
 size_t align_up(size_t x) { return (x + 255) & ~size_t(255); }
@@ -363,8 +447,9 @@ BuildLayout build_layout(int64_t m, int64_t num_nodes, uint32_t options) {
   L.tile_sums = at;  at += align_up(tiles * 8);
   L.raw_col = at;    at += align_up(slots * 4 + 4);
   L.tmp = at;        at += align_up(slots * 4 + 4);
-  L.long_rows = at;  at += align_up((slots / (kSmallRow + 1) + 1) * 4);
-  L.long_count = at; at += align_up(8);
+  L.medium_rows = at; at += align_up((slots / (kSmallRow + 1) + 1) * 4);
+  L.long_rows = at;   at += align_up((slots / (kMediumRow + 1) + 1) * 4);
+  L.list_counts = at; at += align_up(16);
   L.total = at;
   return L;
 }
@@ -436,15 +521,17 @@ int walk_b200_csr_build(const int64_t* src, const int64_t* dst, int64_t num_inpu
   uint64_t* tile_sums = reinterpret_cast<uint64_t*>(base + L.tile_sums);
   uint32_t* raw_col = reinterpret_cast<uint32_t*>(base + L.raw_col);
   uint32_t* tmp = reinterpret_cast<uint32_t*>(base + L.tmp);
+  uint32_t* medium_rows = reinterpret_cast<uint32_t*>(base + L.medium_rows);
   uint32_t* long_rows = reinterpret_cast<uint32_t*>(base + L.long_rows);
-  unsigned long long* long_count = reinterpret_cast<unsigned long long*>(base + L.long_count);
+  unsigned long long* list_counts = reinterpret_cast<unsigned long long*>(base + L.list_counts);
+  unsigned long long* long_count = list_counts + 1;
 
   if (num_nodes == 0 || num_input_edges == 0) {
     WALK_CUDA_TRY(cudaMemsetAsync(rowptr, 0, ((size_t)num_nodes + 1) * 8, s));
     return WALK_B200_OK;
   }
   WALK_CUDA_TRY(cudaMemsetAsync(counters, 0, (size_t)num_nodes * 4, s));
-  WALK_CUDA_TRY(cudaMemsetAsync(long_count, 0, 8, s));
+  WALK_CUDA_TRY(cudaMemsetAsync(list_counts, 0, 16, s));
 
   const unsigned edge_grid = capped_grid((num_input_edges + kBuildBlock - 1) / kBuildBlock, 16);
   csr_edges_kernel<false><<<edge_grid, kBuildBlock, 0, s>>>(src, dst, num_input_edges, num_nodes, options, counters,
@@ -456,14 +543,17 @@ int walk_b200_csr_build(const int64_t* src, const int64_t* dst, int64_t num_inpu
   if (int rc = host::check_launch("csr_edges_kernel<fill>")) return rc;
 
   const unsigned row_grid = capped_grid((num_nodes + kBuildWarps - 1) / kBuildWarps, 16);
-  csr_sort_small_kernel<<<row_grid, kBuildBlock, 0, s>>>(raw_rowptr, num_nodes, options, raw_col, counters, long_rows,
-                                                         long_count);
+  csr_sort_small_kernel<<<row_grid, kBuildBlock, 0, s>>>(raw_rowptr, num_nodes, options, raw_col, counters, medium_rows,
+                                                         long_rows, list_counts);
   if (int rc = host::check_launch("csr_sort_small_kernel")) return rc;
   int key_bits = 1;
   while (key_bits < 31 && (1ll << key_bits) < num_nodes) key_bits++;
   const int passes = (key_bits + 7) / 8;
   const int digit_bits = (key_bits + passes - 1) / passes;
   const unsigned long_grid = (unsigned)host::sm_count() * 8;
+  csr_sort_medium_kernel<<<long_grid, kBuildBlock, 0, s>>>(raw_rowptr, options, passes, digit_bits, raw_col, tmp, counters,
+                                                           medium_rows, list_counts);
+  if (int rc = host::check_launch("csr_sort_medium_kernel")) return rc;
   csr_sort_long_kernel<<<long_grid, kBuildBlock, 0, s>>>(raw_rowptr, options, passes, digit_bits, raw_col, tmp, counters,
                                                          long_rows, long_count);
   if (int rc = host::check_launch("csr_sort_long_kernel")) return rc;
