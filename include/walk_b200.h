@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define WALK_B200_ABI_VERSION 6
+#define WALK_B200_ABI_VERSION 7
 
 /* ---- return codes ---- */
 #define WALK_B200_OK 0
@@ -57,7 +57,7 @@ extern "C" {
                                         node's row instead of the candidate's; results are identical on such graphs */
 
 #define WALK_B200_CSR_WANT_EDGESET 0x2u /* walk_b200_graph_create only: also build the edge hash set and, when rows are
-                                           strictly ascending, the reverse positions */
+                                           strictly ascending, col joined with the reverse positions */
 
 #define WALK_B200_CSR_WANT_FUSED 0x4u /* walk_b200_graph_create only: also build the fused edge records */
 
@@ -72,10 +72,12 @@ typedef struct walk_b200_csr {
   const uint64_t* edgeset; /* device, [4 * edgeset_buckets], from walk_b200_edgeset_build, or NULL: node2vec then
                               runs its membership test as a binary search over col */
   uint64_t edgeset_buckets;
-  const uint32_t* revpos;  /* device, [num_edges], from walk_b200_revpos_build, or NULL; only used together with
-                              edgeset and rowdesc */
+  const uint32_t* revpos;  /* device, [num_edges], from walk_b200_revpos_build, or NULL: input of
+                              walk_b200_colrev_build, not read by the walks */
   const void* fused;       /* device, [num_edges] 16-byte records from walk_b200_fused_build, or NULL; the uniform
                               walk then makes one gather per step; needs rowdesc */
+  const uint64_t* colrev;  /* device, [num_edges], from walk_b200_colrev_build, or NULL; only used together with
+                              edgeset and rowdesc */
 } walk_b200_csr;
 
 /* node2vec instrumentation slots (device uint64[WALK_B200_COUNTER_COUNT], caller zeroes them) */
@@ -189,6 +191,14 @@ int walk_b200_fused_build(const walk_b200_csr* g, void* fused, uint32_t* status_
  * Results are identical with and without it.
  */
 int walk_b200_revpos_build(const walk_b200_csr* g, uint32_t* revpos, uint32_t* status_flags, void* stream);
+
+/*
+ * colrev[e] = col[e] | revpos[e] << 32 (g->revpos must be set; num_nodes < 2^32 - 1; caller scratch
+ * of 8 * num_edges bytes). This is the array the node2vec kernel reads when it uses reverse
+ * positions: the gather of a candidate also brings the position of the edge back from it, so a step
+ * needs no separate look-up of the reverse position. revpos itself may be freed afterwards.
+ */
+int walk_b200_colrev_build(const walk_b200_csr* g, uint64_t* colrev, uint32_t* status_flags, void* stream);
 
 /*
  * Full check the reference never makes (it reinterprets whatever it is given,

@@ -24,7 +24,7 @@ EXPORTS = (
     "walk_b200_abi_version", "walk_b200_last_error", "walk_b200_launch_count",
     "walk_b200_uniform_walk", "walk_b200_uniform_walk_philox", "walk_b200_uniform_draw",
     "walk_b200_uniform_draws", "walk_b200_node2vec_walk", "walk_b200_rowdesc_pack",
-    "walk_b200_csr_validate", "walk_b200_edgeset_buckets", "walk_b200_edgeset_build", "walk_b200_revpos_build", "walk_b200_fused_build", "walk_b200_philox4x32_10", "walk_b200_node2vec_draw",
+    "walk_b200_csr_validate", "walk_b200_edgeset_buckets", "walk_b200_edgeset_build", "walk_b200_revpos_build", "walk_b200_colrev_build", "walk_b200_fused_build", "walk_b200_philox4x32_10", "walk_b200_node2vec_draw",
     "walk_b200_node2vec_thresholds", "walk_b200_shard_range", "walk_b200_shard_count_cyclic",
     "walk_b200_graph_create", "walk_b200_graph_destroy", "walk_b200_graph_csr",
     "walk_b200_graph_device_bytes", "walk_b200_uniform_walk_host", "walk_b200_node2vec_walk_host",
@@ -42,7 +42,7 @@ class Csr(C.Structure):
     _fields_ = [("rowptr", C.c_void_p), ("col", C.c_void_p), ("num_nodes", C.c_int64),
                 ("num_edges", C.c_int64), ("rowdesc", C.c_void_p), ("flags", C.c_uint32),
                 ("reserved", C.c_uint32), ("edgeset", C.c_void_p), ("edgeset_buckets", C.c_uint64),
-                ("revpos", C.c_void_p), ("fused", C.c_void_p)]
+                ("revpos", C.c_void_p), ("fused", C.c_void_p), ("colrev", C.c_void_p)]
 
 
 class WalkError(RuntimeError):
@@ -79,6 +79,7 @@ def lib():
     L.walk_b200_edgeset_buckets.argtypes = [i64, C.POINTER(u64)]
     L.walk_b200_edgeset_build.argtypes = [C.POINTER(Csr), vp, u64, vp, vp]
     L.walk_b200_revpos_build.argtypes = [C.POINTER(Csr), vp, vp, vp]
+    L.walk_b200_colrev_build.argtypes = [C.POINTER(Csr), vp, vp, vp]
     L.walk_b200_fused_build.argtypes = [C.POINTER(Csr), vp, vp, vp]
     L.walk_b200_philox4x32_10.argtypes = [vp, vp, vp]
     L.walk_b200_philox4x32_10.restype = None

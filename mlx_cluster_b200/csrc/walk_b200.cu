@@ -312,7 +312,7 @@ int launch_n2v(const Node2vecParams& P, bool sym, cudaStream_t s) {
   int member = sym ? MEMBER_SEARCH_PREV : MEMBER_SEARCH_CAND;
   if (P.edgeset && P.edgeset_buckets > 0 && g_tuning.n2v_member.load() != 1) member = MEMBER_HASH;
   const bool fits32 = P.num_nodes <= 0x7fffffffll && P.num_edges <= 0xffffffffll;
-  if (member == MEMBER_HASH && P.revpos && P.desc && fits32 && P.num_edges < 0xfffffffell &&
+  if (member == MEMBER_HASH && P.colrev && P.desc && fits32 && P.num_edges < 0xfffffffell &&
       g_tuning.n2v_idx.load() != 1 && rev_pays(P)) {
     const bool e = P.e_out != nullptr, c = P.counters != nullptr;
     if (c) {
@@ -337,7 +337,7 @@ int launch_n2v_host(const Node2vecParams& P, bool sym, cudaStream_t s) {
   const bool e = P.e_out != nullptr;
   int member = sym ? MEMBER_SEARCH_PREV : MEMBER_SEARCH_CAND;
   if (P.edgeset && P.edgeset_buckets > 0 && g_tuning.n2v_member.load() != 1) member = MEMBER_HASH;
-  if (member == MEMBER_HASH && P.revpos && rev_pays(P)) {
+  if (member == MEMBER_HASH && P.colrev && rev_pays(P)) {
     if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, true, false, true, true>, P, s);
     return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, false, false, true, true>, P, s);
   }
@@ -388,7 +388,7 @@ int prepare_n2v(const walk_b200_csr* g, const int64_t* start, int64_t num_walks,
     if ((reinterpret_cast<uintptr_t>(g->edgeset) & 31) != 0)
       return fail(WALK_B200_ERR_INVALID_ARG, "edgeset must be 32-byte aligned");
     P.edgeset = g->edgeset; P.edgeset_buckets = g->edgeset_buckets;
-    P.revpos = g->revpos;
+    P.colrev = g->colrev;
   }
   *out = P;
   return WALK_B200_OK;
@@ -625,6 +625,17 @@ int walk_b200_fused_build(const walk_b200_csr* g, void* fused, uint32_t* status_
   fused_build_kernel<<<grid_for_streaming(g->num_edges), kBlock, 0, (cudaStream_t)stream>>>(
       g->col, g->rowdesc, g->num_nodes, g->num_edges, static_cast<ulonglong2*>(fused), status_flags);
   return check_launch("fused_build_kernel");
+}
+
+int walk_b200_colrev_build(const walk_b200_csr* g, uint64_t* colrev, uint32_t* status_flags, void* stream) {
+  if (int rc = check_csr(g)) return rc;
+  if (!g->revpos) return fail(WALK_B200_ERR_INVALID_ARG, "colrev is built from the reverse positions (revpos is NULL)");
+  if (g->num_edges > 0 && !colrev) return fail(WALK_B200_ERR_INVALID_ARG, "colrev is NULL");
+  if (g->num_nodes >= 0xffffffffll) return fail(WALK_B200_ERR_UNSUPPORTED, "colrev needs num_nodes < 2^32 - 1");
+  if (g->num_edges == 0) return WALK_B200_OK;
+  colrev_build_kernel<<<grid_for_streaming(g->num_edges), kBlock, 0, (cudaStream_t)stream>>>(
+      g->col, g->revpos, g->num_nodes, g->num_edges, colrev, status_flags);
+  return check_launch("colrev_build_kernel");
 }
 
 int walk_b200_revpos_build(const walk_b200_csr* g, uint32_t* revpos, uint32_t* status_flags, void* stream) {
@@ -881,7 +892,7 @@ struct walk_b200_graph {
   uint64_t* d_desc = nullptr;
   uint64_t* d_edgeset = nullptr;
   uint64_t edgeset_buckets = 0;
-  uint32_t* d_revpos = nullptr;
+  uint64_t* d_colrev = nullptr;
   void* d_fused = nullptr;
   uint32_t* d_flags = nullptr;
   static constexpr int kLanes = 4;  // slabs in flight: copy-in, kernel, copy-out, host widening
@@ -1128,7 +1139,7 @@ int run_host_walk(walk_b200_graph* g, bool biased, const int64_t* h_start, const
   csr.rowptr = g->d_rowptr; csr.col = g->d_col; csr.num_nodes = g->num_nodes; csr.num_edges = g->num_edges;
   csr.rowdesc = g->d_desc; csr.flags = g->csr_flags;
   csr.edgeset = g->d_edgeset; csr.edgeset_buckets = g->edgeset_buckets;
-  csr.revpos = g->d_revpos;
+  csr.colrev = g->d_colrev;
   csr.fused = g->d_fused;
 
   if (biased && narrow && g_tuning.host_single_launch.load() != 0) {
@@ -1275,15 +1286,21 @@ int walk_b200_graph_create(const int64_t* h_rowptr, const int64_t* h_col, int64_
     if (f) { flags_to_status(f); return bail(fail(WALK_B200_ERR_CSR_INVALID, "edge set build failed: %s", std::string(g_last_error).c_str())); }
     // reverse positions ride on the edge set; rows that are not strictly ascending simply go without
     if (num_edges < 0xfffffffell) {
-      G_TRY(cudaMalloc((void**)&g->d_revpos, (size_t)num_edges * sizeof(uint32_t)));
-      if (int rc = walk_b200_revpos_build(&csr, g->d_revpos, g->d_flags, s)) return bail(rc);
-      G_TRY(cudaMemcpyAsync(&f, g->d_flags, 4, cudaMemcpyDeviceToHost, s));
-      G_TRY(cudaStreamSynchronize(s));
-      if (f) {
-        cudaFree(g->d_revpos);
-        g->d_revpos = nullptr;
-        G_TRY(cudaMemsetAsync(g->d_flags, 0, 4, s));
+      uint32_t* d_revpos = nullptr;
+      G_TRY(cudaMalloc((void**)&d_revpos, (size_t)num_edges * sizeof(uint32_t)));
+      int rc = walk_b200_revpos_build(&csr, d_revpos, g->d_flags, s);
+      cudaError_t ce = rc ? cudaSuccess : cudaMemcpyAsync(&f, g->d_flags, 4, cudaMemcpyDeviceToHost, s);
+      if (!rc && ce == cudaSuccess) ce = cudaStreamSynchronize(s);
+      if (!rc && ce == cudaSuccess && !f) {  // join them with col: the array the kernel gathers from
+        csr.revpos = d_revpos;
+        ce = cudaMalloc((void**)&g->d_colrev, (size_t)num_edges * sizeof(uint64_t));
+        if (ce == cudaSuccess) rc = walk_b200_colrev_build(&csr, g->d_colrev, g->d_flags, s);
+        if (!rc && ce == cudaSuccess) ce = cudaStreamSynchronize(s);
       }
+      cudaFree(d_revpos);
+      if (rc) return bail(rc);
+      if (ce != cudaSuccess) return bail(fail(WALK_B200_ERR_CUDA, "reverse-position build failed: %s", cudaGetErrorString(ce)));
+      if (f) G_TRY(cudaMemsetAsync(g->d_flags, 0, 4, s));
     }
   }
   if ((csr_flags & WALK_B200_CSR_WANT_FUSED) && num_edges > 0 && g->d_desc) {
@@ -1322,7 +1339,7 @@ int walk_b200_graph_destroy(walk_b200_graph* g) {
     if (g->d_col) cudaFree(g->d_col);
     if (g->d_desc) cudaFree(g->d_desc);
     if (g->d_edgeset) cudaFree(g->d_edgeset);
-    if (g->d_revpos) cudaFree(g->d_revpos);
+    if (g->d_colrev) cudaFree(g->d_colrev);
     if (g->d_fused) cudaFree(g->d_fused);
     if (g->d_flags) cudaFree(g->d_flags);
     if (g->d_start_all) cudaFree(g->d_start_all);
@@ -1341,7 +1358,7 @@ int walk_b200_graph_csr(const walk_b200_graph* g, walk_b200_csr* out) {
   out->rowptr = g->d_rowptr; out->col = g->d_col; out->num_nodes = g->num_nodes; out->num_edges = g->num_edges;
   out->rowdesc = g->d_desc; out->flags = g->csr_flags;
   out->edgeset = g->d_edgeset; out->edgeset_buckets = g->edgeset_buckets;
-  out->revpos = g->d_revpos;
+  out->colrev = g->d_colrev;
   out->fused = g->d_fused;
   return WALK_B200_OK;
 }
@@ -1350,7 +1367,7 @@ int walk_b200_graph_device_bytes(const walk_b200_graph* g, int64_t* bytes) {
   if (!g || !bytes) return fail(WALK_B200_ERR_INVALID_ARG, "graph or bytes is NULL");
   *bytes = (g->num_nodes + 1) * 8 + g->num_edges * 8 + (g->d_desc ? g->num_nodes * 8 : 0) +
            (int64_t)(g->d_edgeset ? g->edgeset_buckets * kEdgeSlotsPerBucket * 8 : 0) +
-           (g->d_revpos ? g->num_edges * 4 : 0) + (g->d_fused ? g->num_edges * 16 : 0);
+           (g->d_colrev ? g->num_edges * 8 : 0) + (g->d_fused ? g->num_edges * 16 : 0);
   return WALK_B200_OK;
 }
 

@@ -211,6 +211,25 @@ __global__ void __launch_bounds__(kBlock) fused_build_kernel(const int64_t* __re
   }
 }
 
+// col and reverse position in one 8-byte word: colrev[e] = col[e] | revpos[e] << 32. The gather of a
+// candidate then also brings the position of the edge back from it, which is what the step after an
+// accepted candidate needs; the separate 4-byte gather of revpos per step disappears.
+__global__ void __launch_bounds__(kBlock) colrev_build_kernel(const int64_t* __restrict__ col,
+                                                              const uint32_t* __restrict__ revpos,
+                                                              int64_t num_nodes, int64_t num_edges,
+                                                              uint64_t* __restrict__ colrev, uint32_t* flags) {
+  const int64_t stride = (int64_t)gridDim.x * kBlock;
+  for (int64_t e = (int64_t)blockIdx.x * kBlock + threadIdx.x; e < num_edges; e += stride) {
+    const int64_t c = col[e];
+    if ((uint64_t)c >= (uint64_t)num_nodes) {
+      raise_flag(flags, WALK_B200_FLAG_BAD_NODE);
+      colrev[e] = 0xffffffffull | (0xfffffffeull << 32);  // out of range for the walk to flag; edge back unknown
+    } else {
+      colrev[e] = (uint64_t)(uint32_t)c | ((uint64_t)revpos[e] << 32);
+    }
+  }
+}
+
 struct UniformParams {
   const int64_t* rowptr;
   const int64_t* col;
@@ -526,7 +545,7 @@ struct Node2vecParams {
   const uint64_t* desc;
   const uint64_t* edgeset;
   uint64_t edgeset_buckets;
-  const uint32_t* revpos;
+  const uint64_t* colrev;  // REV kernels: col[e] | revpos[e] << 32
   int64_t num_nodes, num_edges;
   const int64_t* start;
   int64_t num_walks;
@@ -586,11 +605,13 @@ enum : int { MEMBER_SEARCH_PREV = 0, MEMBER_SEARCH_CAND = 1, MEMBER_HASH = 2 };
 // MEMBER_HASH asks the edge hash set for (x -> t).
 //
 // REV (with MEMBER_HASH, row descriptors and 32-bit indices): the lane also carries ret_e, the
-// index in col of the edge back to the previous node (one 4-byte revpos load riding along with
-// the row fetch). An attempt whose drawn edge is ret_e knows its candidate (x = t) without a
-// gather, and an attempt whose accept draw is >= cut1 can only be accepted by the return rule:
-// if its edge is not ret_e it is rejected without touching memory at all. At (p, q) = (0.25, 4)
-// that is three attempts in four. Same draws, same decisions, fewer gathers.
+// index in col of the edge back to the previous node, and in_e, the index of the edge it arrived by.
+// Candidates are gathered from colrev, whose upper half is the position of the edge back from the
+// candidate: accepting it makes that the next ret_e. An attempt whose drawn edge is ret_e knows its
+// candidate (x = t) without a gather, and accepting it just swaps ret_e and in_e; an attempt whose
+// accept draw is >= cut1 can only be accepted by the return rule: if its edge is not ret_e it is
+// rejected without touching memory at all. At (p, q) = (0.25, 4) that is three attempts in four.
+// Same draws, same decisions, fewer gathers.
 //
 // HOST (the host-buffer entry point's single-launch mode): the walk and edge matrices are int32
 // (P.n_out / P.e_out point at int32 storage; the ids fit) and finished walks are counted per slab of
@@ -624,6 +645,8 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
   uidx_t lo = 0, hi = 0;          // search window / hash bucket + probe count / parked accept draw
   idx_t e = 0;                    // sampled edge index
   idx_t ret_e = (idx_t)kUnknownEdge;  // REV: index of the edge v -> t (kNoEdge: there is none)
+  idx_t in_e = (idx_t)kUnknownEdge;   // REV: index of the edge t -> v the walk arrived by
+  uint32_t x_rev = kUnknownEdge;      // REV: index of the edge x -> v, gathered with the candidate x
   int32_t l = 0;                  // step being produced
   uint32_t a = 0;                 // attempt counter of this step
   int state = ST_IDLE;
@@ -702,6 +725,11 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
       if (state == ST_ACCEPTED) {  // write the decided step, advance, go on to the next row fetch
         put_node(i, l + 1, (int64_t)x);
         if (HAS_EOUT) put_edge(i, l, (a >= P.max_attempts) ? -1 : (int64_t)e);
+        if (REV) {
+          if (e == (idx_t)kUnknownEdge) { ret_e = (idx_t)kUnknownEdge; in_e = (idx_t)kUnknownEdge; }  // stood still
+          else if (e == ret_e) { const idx_t back = ret_e; ret_e = in_e; in_e = back; }              // went back
+          else { in_e = e; ret_e = (idx_t)x_rev; }
+        }
         t = v; t_rs = v_rs; t_re = v_re;
         v = x;
         l++;
@@ -740,7 +768,7 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
           }
           lo = acc;  // parked until the candidate arrives
         }
-        addr = col + (int64_t)e;
+        addr = REV ? (const void*)(P.colrev + (int64_t)e) : (const void*)(col + (int64_t)e);
         if (REV && l > 0 && ret_e != (idx_t)kUnknownEdge) {
           const bool is_ret = (e == ret_e);
           if (v_deg == 1) {
@@ -774,7 +802,6 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
       }
 
       int64_t val = 0, val2 = 0;
-      uint32_t rev = kUnknownEdge;
       ulonglong2 h0 = {0, 0}, h1 = {0, 0};
       if (!need_load) {
         // decided above
@@ -789,9 +816,9 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
         // the instrumented kernel's extra look at deg(x) is bookkeeping, not part of the walk
         const bool bookkeeping = COUNT && state == ST_XROW && MEMBER != MEMBER_SEARCH_CAND;
         if (COUNT && !bookkeeping) c_loads += pair ? 2 : 1;
-        if (REV && state == ST_ROW && l > 0 && e != (idx_t)kUnknownEdge) {
-          rev = ld4(P.revpos + (int64_t)e, policy);
-          if (COUNT) c_loads += 1;
+        if (REV && state == ST_ATTEMPT) {
+          x_rev = (uint32_t)((uint64_t)val >> 32);
+          val = (int64_t)((uint64_t)val & 0xffffffffull);
         }
       }
 
@@ -803,6 +830,7 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
         t = (idx_t)val;
         v = (idx_t)val;
         l = 0;
+        if (REV) { ret_e = (idx_t)kUnknownEdge; in_e = (idx_t)kUnknownEdge; }
         if ((uint64_t)val >= (uint64_t)P.num_nodes) {
           raise_flag(P.flags, WALK_B200_FLAG_BAD_NODE);
           for (int32_t k = 0; k < L; k++) { put_node(i, k + 1, val); if (HAS_EOUT) put_edge(i, k, -1); }
@@ -832,7 +860,6 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
             v_deg = deg > 0x7fffffffll ? 0x80000000u : (uint32_t)deg;
             v_inv = 0xffffffffu / v_deg;
             a = 0;
-            if (REV) ret_e = (idx_t)rev;
             state = ST_ATTEMPT;
             if (COUNT) { if (l == 0) c_first++; else if (deg == 1) c_deg1++; else c_sampled++; }
           }
@@ -858,6 +885,7 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
         if ((uint64_t)val >= (uint64_t)P.num_nodes) {
           raise_flag(P.flags, WALK_B200_FLAG_BAD_NODE);
           val = (int64_t)v;  // park on the current node
+          if (REV) x_rev = kUnknownEdge;
         }
         x = (idx_t)val;
         if (l == 0 || v_deg == 1) {

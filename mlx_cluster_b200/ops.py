@@ -74,7 +74,7 @@ class WalkGraph:
         self.rowdesc = None
         self.edgeset = None
         self.edgeset_buckets = 0
-        self.revpos = None
+        self.colrev = None
         self.fused = None
         self._version = (rowptr._version, col._version)
         with torch.cuda.device(dev):
@@ -130,20 +130,28 @@ class WalkGraph:
             if f:
                 raise ValueError(f"edge set build failed, status flags 0x{f:x}: {describe_flags(f)}")
             self.edgeset, self.edgeset_buckets = table, buckets
-            # reverse positions ride along when they can be built (rows strictly ascending, < 2^32 - 2 edges)
-            if self.num_edges < 2**32 - 2 and self.rowdesc is not None:
+            # reverse positions ride along when they can be built (rows strictly ascending, < 2^32 - 2
+            # edges); they are joined with col into the one array the kernel gathers candidates from
+            if self.num_edges < 2**32 - 2 and self.rowdesc is not None and self.num_nodes < 2**32 - 1:
                 rev = torch.empty(self.num_edges, dtype=torch.int32, device=self.device)
-                _lib.check(_lib.lib().walk_b200_revpos_build(C.byref(csr), rev.data_ptr(), self.flags.data_ptr(),
-                                                             _stream_handle(stream, self.device)))
+                sh = _stream_handle(stream, self.device)
+                _lib.check(_lib.lib().walk_b200_revpos_build(C.byref(csr), rev.data_ptr(), self.flags.data_ptr(), sh))
                 f = int(self.flags.item())
                 self.flags.zero_()
                 if not f:
-                    self.revpos = rev
+                    csr.revpos = rev.data_ptr()
+                    joined = torch.empty(self.num_edges, dtype=torch.int64, device=self.device)
+                    _lib.check(_lib.lib().walk_b200_colrev_build(C.byref(csr), joined.data_ptr(), self.flags.data_ptr(), sh))
+                    f = int(self.flags.item())
+                    self.flags.zero_()
+                    if f:
+                        raise ValueError(f"colrev build failed, status flags 0x{f:x}: {describe_flags(f)}")
+                    self.colrev = joined
 
     def csr(self) -> _lib.Csr:
         return _lib.Csr(self.rowptr.data_ptr(), _ptr(self.col), self.num_nodes, self.num_edges,
                         _ptr(self.rowdesc), _lib.CSR_SYMMETRIC if self.symmetric else 0, 0,
-                        _ptr(self.edgeset), self.edgeset_buckets, _ptr(self.revpos), _ptr(self.fused))
+                        _ptr(self.edgeset), self.edgeset_buckets, None, _ptr(self.fused), _ptr(self.colrev))
 
     def validate(self, start: Optional[torch.Tensor] = None, *, check_sorted: bool = True, stream=None):
         """Raise ValueError when the CSR (and, if given, the start nodes) is malformed."""

@@ -122,7 +122,7 @@ def test_host_entry_reports_bad_input(cuda, golden):
     assert hg.device_bytes() == (2709 + 10556 + 2708) * 8
     hg.close()
     hg = HostGraph(g["rowptr1"], g["col1"], edgeset=True)
-    assert hg.device_bytes() == (2709 + 10556 + 2708) * 8 + _lib.edgeset_buckets(10556) * 32 + 10556 * 4
+    assert hg.device_bytes() == (2709 + 10556 + 2708) * 8 + _lib.edgeset_buckets(10556) * 32 + 10556 * 8
     hg.close()
 
 

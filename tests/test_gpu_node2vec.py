@@ -162,7 +162,7 @@ def test_unsorted_rows_fall_back_to_the_hash_set_alone(cuda):
         rng.shuffle(col[rowptr[v]:rowptr[v + 1]])
     start = rng.integers(0, 400, 3000).astype(np.int64)
     g = WalkGraph(torch.from_numpy(rowptr).to(cuda), torch.from_numpy(col).to(cuda), edgeset=True)
-    assert g.edgeset is not None and g.revpos is None
+    assert g.edgeset is not None and g.colrev is None
     for pq in [(0.25, 4.0), (2.0, 0.5)]:
         want = oracle.node2vec_walk(rowptr, col, start, 25, *pq, seed=2)
         got = rejection_sampling(None, None, torch.from_numpy(start).to(cuda), 25, *pq, graph=g, seed=2, check=True)
@@ -170,7 +170,7 @@ def test_unsorted_rows_fall_back_to_the_hash_set_alone(cuda):
     sorted_graph = WalkGraph(torch.from_numpy(rowptr).to(cuda),
                              torch.from_numpy(np.concatenate([np.sort(col[rowptr[v]:rowptr[v + 1]]) for v in range(400)])).to(cuda),
                              edgeset=True)
-    assert sorted_graph.revpos is not None
+    assert sorted_graph.colrev is not None
 
 
 def test_medium_rmat_stream_exact(cuda):
@@ -187,7 +187,7 @@ def test_medium_rmat_stream_exact(cuda):
             assert c["attempts"] == cnt["attempts"] and c["membership"] == cnt["membership_needed"]
             assert c["formula_probes"] == cnt["bsearch_probes"]
         hashed = WalkGraph(rowptr, col, edgeset=True)
-        assert hashed.revpos is not None
+        assert hashed.colrev is not None
         loads = {}
         for rev in (1, 0):
             _lib.set_tuning("n2v_rev", 2 if rev else 0)
