@@ -46,8 +46,8 @@ RMAT = dict(a=0.57, b=0.19, c=0.19, d=0.05)
 # profiles/: measured on the scale-20 case of each workload; the full-size figures are that measurement
 # scaled by the number of gathers issued (traffic is proportional to gathers; see the profile notes).
 NCU_TRAFFIC = {
-    "node2vec_rmat20": (24.31e9, "ncu, measured"),
-    "node2vec_rmat24": (24.31e9 * 14.75, "ncu on node2vec_rmat20 scaled by gathers issued (x14.75)"),
+    "node2vec_rmat20": (18.16e9, "ncu, measured"),
+    "node2vec_rmat24": (18.16e9 * 14.90, "ncu on node2vec_rmat20 scaled by gathers issued (x14.90)"),
     "uniform_rmat20": (4.70e9, "ncu, measured"),
     "uniform_rmat22": (4.70e9 * 3.72, "ncu on uniform_rmat20 scaled by gathers issued (x3.72)"),
 }
