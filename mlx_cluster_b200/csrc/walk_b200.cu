@@ -20,6 +20,7 @@
 #include "host_common.h"
 #include "host_widen.h"
 #include "walk_kernels.cuh"
+#include "n2v_pool.cuh"
 
 namespace {
 
@@ -65,6 +66,7 @@ struct Tuning {
   std::atomic<int32_t> n2v_draw_loop{3};    // memory-free rejections consumed per trip (reverse-position kernel;
                                             // measured: 1 -> 193 ms, 2 -> 169, 3 -> 166, 4 -> 170, 8 -> 207)
   std::atomic<int32_t> n2v_rev{1};          // 1 auto (reverse positions when they pay), 0 never, 2 whenever available
+  std::atomic<int32_t> n2v_pool{0};         // 1: pooled kernel (walk state in shared memory, one state class per trip)
   std::atomic<int32_t> n2v_blocks_per_sm{0};  // 0 = what the occupancy calculator allows
   std::atomic<int32_t> l2_hints{3};         // bit 0: evict-last row bounds, bit 1: evict-first streams
   std::atomic<int32_t> l2_fetch_granularity{0};  // set only through walk_b200_set_tuning (applies the CUDA limit)
@@ -84,6 +86,7 @@ std::atomic<int32_t>* tuning_slot(const char* key) {
   if (!strcmp(key, "n2v_idx")) return &g_tuning.n2v_idx;
   if (!strcmp(key, "n2v_member")) return &g_tuning.n2v_member;
   if (!strcmp(key, "n2v_rev")) return &g_tuning.n2v_rev;
+  if (!strcmp(key, "n2v_pool")) return &g_tuning.n2v_pool;
   if (!strcmp(key, "n2v_batch_lanes")) return &g_tuning.n2v_batch_lanes;
   if (!strcmp(key, "n2v_batch_trips")) return &g_tuning.n2v_batch_trips;
   if (!strcmp(key, "n2v_draw_loop")) return &g_tuning.n2v_draw_loop;
@@ -308,9 +311,21 @@ bool rev_pays(const Node2vecParams& P) {
   return top <= (1u << 30);  // max(prob_1, prob_2) <= 0.5
 }
 
+// The pooled kernel covers the configuration with every per-graph structure present.
+bool pool_applies(const Node2vecParams& P, int member) {
+  return g_tuning.n2v_pool.load() != 0 && member == MEMBER_HASH && P.colrev && P.desc && !P.counters &&
+         P.num_nodes <= 0x7fffffffll && P.num_edges < 0xfffffffell && P.edgeset_buckets < 0xffffffffull &&
+         P.num_walks < 0xffffffffll && P.walk_length < 65536 && g_tuning.n2v_idx.load() != 1 &&
+         g_tuning.n2v_rev.load() != 0;
+}
+
 int launch_n2v(const Node2vecParams& P, bool sym, cudaStream_t s) {
   int member = sym ? MEMBER_SEARCH_PREV : MEMBER_SEARCH_CAND;
   if (P.edgeset && P.edgeset_buckets > 0 && g_tuning.n2v_member.load() != 1) member = MEMBER_HASH;
+  if (pool_applies(P, member)) {
+    if (P.e_out) return launch_n2v_kernel(node2vec_pool_kernel<true, false>, P, s);
+    return launch_n2v_kernel(node2vec_pool_kernel<false, false>, P, s);
+  }
   const bool fits32 = P.num_nodes <= 0x7fffffffll && P.num_edges <= 0xffffffffll;
   if (member == MEMBER_HASH && P.colrev && P.desc && fits32 && P.num_edges < 0xfffffffell &&
       g_tuning.n2v_idx.load() != 1 && rev_pays(P)) {
@@ -337,6 +352,10 @@ int launch_n2v_host(const Node2vecParams& P, bool sym, cudaStream_t s) {
   const bool e = P.e_out != nullptr;
   int member = sym ? MEMBER_SEARCH_PREV : MEMBER_SEARCH_CAND;
   if (P.edgeset && P.edgeset_buckets > 0 && g_tuning.n2v_member.load() != 1) member = MEMBER_HASH;
+  if (pool_applies(P, member)) {
+    if (e) return launch_n2v_kernel(node2vec_pool_kernel<true, true>, P, s);
+    return launch_n2v_kernel(node2vec_pool_kernel<false, true>, P, s);
+  }
   if (member == MEMBER_HASH && P.colrev && rev_pays(P)) {
     if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, true, false, true, true>, P, s);
     return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, false, false, true, true>, P, s);

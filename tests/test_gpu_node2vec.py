@@ -22,13 +22,15 @@ def _reset_tuning():
     yield
     _lib.set_tuning("n2v_idx", 0)
     _lib.set_tuning("n2v_rev", 1)
+    _lib.set_tuning("n2v_pool", 0)
     _lib.set_tuning("l2_hints", 3)
 
 
 def run_gpu(dev, rowptr, col, start, L, p, q, *, seed=0, base=0, symmetric=False, rowdesc=True,
-            idx64=False, edges=True, counters=False, edgeset=False, rev=True):
+            idx64=False, edges=True, counters=False, edgeset=False, rev=True, pool=False):
     _lib.set_tuning("n2v_idx", 1 if idx64 else 0)
     _lib.set_tuning("n2v_rev", 2 if rev else 0)
+    _lib.set_tuning("n2v_pool", 1 if pool else 0)
     g = WalkGraph(torch.from_numpy(rowptr).to(dev), torch.from_numpy(col).to(dev), symmetric=symmetric,
                   use_rowdesc=rowdesc, edgeset=edgeset)
     assert (g.edgeset is not None) == (edgeset and col.size > 0)
@@ -40,7 +42,8 @@ def run_gpu(dev, rowptr, col, start, L, p, q, *, seed=0, base=0, symmetric=False
 
 
 MEMBERSHIP = {"search_candidate_row": dict(symmetric=False), "search_previous_row": dict(symmetric=True),
-              "edge_hash_set": dict(edgeset=True, rev=False), "edge_hash_set_and_reverse_positions": dict(edgeset=True)}
+              "edge_hash_set": dict(edgeset=True, rev=False), "edge_hash_set_and_reverse_positions": dict(edgeset=True),
+              "pooled_kernel": dict(edgeset=True, pool=True)}
 
 
 @pytest.mark.parametrize("pq", PQS)
@@ -126,9 +129,11 @@ def test_ragged_shapes_and_directed_graphs(cuda, symmetric, edgeset):
                 np.testing.assert_array_equal(n[:, 0], start)
                 continue
             n_o, e_o = oracle.node2vec_walk(rowptr, col, start, L, *pq, seed=trial, return_edges=True)
-            n, e = run_gpu(cuda, rowptr, col, start, L, *pq, seed=trial, symmetric=symmetric, edgeset=edgeset)
-            np.testing.assert_array_equal(n, n_o, err_msg=f"trial {trial} pq {pq}")
-            np.testing.assert_array_equal(e, e_o, err_msg=f"trial {trial} pq {pq}")
+            for pool in ((False, True) if edgeset else (False,)):
+                n, e = run_gpu(cuda, rowptr, col, start, L, *pq, seed=trial, symmetric=symmetric, edgeset=edgeset,
+                               pool=pool)
+                np.testing.assert_array_equal(n, n_o, err_msg=f"trial {trial} pq {pq} pool {pool}")
+                np.testing.assert_array_equal(e, e_o, err_msg=f"trial {trial} pq {pq} pool {pool}")
 
 
 def test_self_loops_and_degree_one_chains(cuda):
@@ -138,10 +143,13 @@ def test_self_loops_and_degree_one_chains(cuda):
     start = np.array([0, 1, 2, 3] * 40, dtype=np.int64)
     for pq in PQS:
         n_o, e_o = oracle.node2vec_walk(rowptr, col, start, 30, *pq, seed=3, return_edges=True)
-        for edgeset in (False, True):
-            n, e = run_gpu(cuda, rowptr, col, start, 30, *pq, seed=3, symmetric=False, edgeset=edgeset)
+        for edgeset, pool in ((False, False), (True, False), (True, True)):
+            n, e = run_gpu(cuda, rowptr, col, start, 30, *pq, seed=3, symmetric=False, edgeset=edgeset, pool=pool)
             np.testing.assert_array_equal(n, n_o)
             np.testing.assert_array_equal(e, e_o)
+            n = run_gpu(cuda, rowptr, col, start, 30, *pq, seed=3, symmetric=False, edgeset=edgeset, pool=pool,
+                        edges=False)
+            np.testing.assert_array_equal(n, n_o)
     m = 50
     src = np.arange(m - 1)
     rp, cl = graphs.edges_to_csr(torch.from_numpy(src), torch.from_numpy(src + 1), m)
@@ -188,6 +196,10 @@ def test_medium_rmat_stream_exact(cuda):
             assert c["formula_probes"] == cnt["bsearch_probes"]
         hashed = WalkGraph(rowptr, col, edgeset=True)
         assert hashed.colrev is not None
+        _lib.set_tuning("n2v_pool", 1)
+        out = rejection_sampling(None, None, start, 40, *pq, graph=hashed, seed=77, check=True)
+        np.testing.assert_array_equal(out.cpu().numpy(), n_o)
+        _lib.set_tuning("n2v_pool", 0)
         loads = {}
         for rev in (1, 0):
             _lib.set_tuning("n2v_rev", 2 if rev else 0)
