@@ -66,7 +66,7 @@ struct Tuning {
   std::atomic<int32_t> n2v_draw_loop{3};    // memory-free rejections consumed per trip (reverse-position kernel;
                                             // measured: 1 -> 193 ms, 2 -> 169, 3 -> 166, 4 -> 170, 8 -> 207)
   std::atomic<int32_t> n2v_rev{1};          // 1 auto (reverse positions when they pay), 0 never, 2 whenever available
-  std::atomic<int32_t> n2v_pool{0};         // 1: pooled kernel (walk state in shared memory, one state class per trip)
+  std::atomic<int32_t> n2v_pool{1};         // 1: pooled kernel (walk state in shared memory, one state class per trip)
   std::atomic<int32_t> n2v_blocks_per_sm{0};  // 0 = what the occupancy calculator allows
   std::atomic<int32_t> l2_hints{3};         // bit 0: evict-last row bounds, bit 1: evict-first streams
   std::atomic<int32_t> l2_fetch_granularity{0};  // set only through walk_b200_set_tuning (applies the CUDA limit)
@@ -311,9 +311,13 @@ bool rev_pays(const Node2vecParams& P) {
   return top <= (1u << 30);  // max(prob_1, prob_2) <= 0.5
 }
 
-// The pooled kernel covers the configuration with every per-graph structure present.
+// The pooled kernel covers the configuration with every per-graph structure present. It wins where
+// steps are long (many rejected attempts per step, i.e. where the reverse positions pay: 123 vs
+// 164 ms at (p, q) = (0.25, 4) on R-MAT 24) and loses where almost every first candidate is accepted
+// and a step is three short trips (8.9 vs 7.9 ms at (1, 2) on R-MAT 22): 1 = where it wins, 2 = always.
 bool pool_applies(const Node2vecParams& P, int member) {
-  return g_tuning.n2v_pool.load() != 0 && member == MEMBER_HASH && P.colrev && P.desc && !P.counters &&
+  const int mode = g_tuning.n2v_pool.load();
+  return mode != 0 && (mode == 2 || rev_pays(P)) && member == MEMBER_HASH && P.colrev && P.desc && !P.counters &&
          P.num_nodes <= 0x7fffffffll && P.num_edges < 0xfffffffell && P.edgeset_buckets < 0xffffffffull &&
          P.num_walks < 0xffffffffll && P.walk_length < 65536 && g_tuning.n2v_idx.load() != 1 &&
          g_tuning.n2v_rev.load() != 0;
@@ -1041,9 +1045,10 @@ int run_host_n2v_single(walk_b200_graph* g, const walk_b200_csr& csr, const int6
   if (need > ((size_t)g_tuning.host_resident_mb.load() << 20)) return kNoHostKernel;
   if (g_tuning.n2v_idx.load() == 1) return kNoHostKernel;
 
-  // slab: the largest power of two of rows whose int32 copy is at most a quarter of the slab tuning
+  // slab: the largest power of two of rows whose int32 copy is at most an eighth of the slab tuning
+  // (small slabs keep the staging copy cache-warm for the widening threads and shorten the exposed tail)
   int shift = 10;
-  const size_t target = ((size_t)g_tuning.host_slab_mb.load() << 20) / 4;
+  const size_t target = ((size_t)g_tuning.host_slab_mb.load() << 20) / 8;
   while (shift < 30 && ((size_t)2 << shift) * row32 <= target) shift++;
   const int64_t slab_rows = (int64_t)1 << shift;
   const int64_t slabs = (n + slab_rows - 1) / slab_rows;

@@ -20,7 +20,7 @@ def _reset():
     _lib.set_tuning("host_narrow", 1)
     _lib.set_tuning("host_threads", 0)
     _lib.set_tuning("host_single_launch", 1)
-    _lib.set_tuning("n2v_pool", 0)
+    _lib.set_tuning("n2v_pool", 1)
     clear_caches()
 
 
@@ -97,7 +97,7 @@ def test_narrow_transport_is_invisible(cuda):
             out, e = rejection_sampling(rowptr, col, start, L, 0.25, 4.0, seed=3, return_edges=True, **kw)
             np.testing.assert_array_equal(out.numpy(), want_b)
             np.testing.assert_array_equal(e.numpy(), want_be)
-        for pool in (1, 0):
+        for pool in (2, 0):
             _lib.set_tuning("n2v_pool", pool)
             out = rejection_sampling(rowptr, col, start, L, 0.25, 4.0, seed=3, edgeset=True)
             np.testing.assert_array_equal(out.numpy(), want_b)

@@ -22,7 +22,7 @@ def _reset_tuning():
     yield
     _lib.set_tuning("n2v_idx", 0)
     _lib.set_tuning("n2v_rev", 1)
-    _lib.set_tuning("n2v_pool", 0)
+    _lib.set_tuning("n2v_pool", 1)
     _lib.set_tuning("l2_hints", 3)
 
 
@@ -30,7 +30,7 @@ def run_gpu(dev, rowptr, col, start, L, p, q, *, seed=0, base=0, symmetric=False
             idx64=False, edges=True, counters=False, edgeset=False, rev=True, pool=False):
     _lib.set_tuning("n2v_idx", 1 if idx64 else 0)
     _lib.set_tuning("n2v_rev", 2 if rev else 0)
-    _lib.set_tuning("n2v_pool", 1 if pool else 0)
+    _lib.set_tuning("n2v_pool", 2 if pool else 0)
     g = WalkGraph(torch.from_numpy(rowptr).to(dev), torch.from_numpy(col).to(dev), symmetric=symmetric,
                   use_rowdesc=rowdesc, edgeset=edgeset)
     assert (g.edgeset is not None) == (edgeset and col.size > 0)
@@ -196,7 +196,7 @@ def test_medium_rmat_stream_exact(cuda):
             assert c["formula_probes"] == cnt["bsearch_probes"]
         hashed = WalkGraph(rowptr, col, edgeset=True)
         assert hashed.colrev is not None
-        _lib.set_tuning("n2v_pool", 1)
+        _lib.set_tuning("n2v_pool", 2)
         out = rejection_sampling(None, None, start, 40, *pq, graph=hashed, seed=77, check=True)
         np.testing.assert_array_equal(out.cpu().numpy(), n_o)
         _lib.set_tuning("n2v_pool", 0)
