@@ -13,7 +13,8 @@
 
 namespace walk_b200 {
 
-constexpr int kPoolSlots = 64;  // walk slots per warp
+constexpr int kPoolSlots = 64;  // walk slots per warp. Measured at R-MAT 24, (0.25, 4): 32 slots 141 ms, 64 slots 124 ms,
+                                // 96 slots 181 ms (its shared memory leaves the SM too little L1 for the misses in flight)
 enum : int {
   PF_I = 0,   // walk (row of this launch)
   PF_T,       // previous node
@@ -33,10 +34,11 @@ enum : int {
 };
 enum : int { PS_IDLE = 0, PS_START, PS_ROW, PS_ACCEPTED, PS_ATTEMPT, PS_HASH };
 
-template <bool HAS_EOUT, bool HOST>
+template <bool HAS_EOUT, bool HOST, int SLOTS = kPoolSlots>
 __global__ void __launch_bounds__(kBlock, 6) node2vec_pool_kernel(const Node2vecParams P) {
-  __shared__ uint32_t pool[PF_COUNT][kWarpsPerBlock][kPoolSlots];
-  __shared__ uint8_t sel[kWarpsPerBlock][32];
+  static_assert(SLOTS % 32 == 0 && SLOTS >= 32 && SLOTS <= 96, "whole slots per lane, within static shared memory");
+  __shared__ uint32_t pool[PF_COUNT][kWarpsPerBlock][SLOTS];
+  __shared__ uint8_t sel[kWarpsPerBlock][SLOTS];
   constexpr unsigned kFull = 0xffffffffu;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const unsigned lt = (1u << lane) - 1u;
@@ -66,20 +68,27 @@ __global__ void __launch_bounds__(kBlock, 6) node2vec_pool_kernel(const Node2vec
     }
   };
 
-  FLD(PF_LS, lane) = PS_IDLE;
-  FLD(PF_LS, lane + 32) = PS_IDLE;
+  constexpr int K = SLOTS / 32;  // slots per lane: slot lane + 32 k, k < K
+#pragma unroll
+  for (int k = 0; k < K; k++) FLD(PF_LS, lane + 32 * k) = PS_IDLE;
   __syncwarp();
   int64_t q_next = 0, q_end = 0;  // current chunk of 32 walks of the launch-wide queue
   bool drained = false;
 
   while (true) {
-    int s0 = (int)(FLD(PF_LS, lane) & 7u), s1 = (int)(FLD(PF_LS, lane + 32) & 7u);
+    int st[K];
+#pragma unroll
+    for (int k = 0; k < K; k++) st[k] = (int)(FLD(PF_LS, lane + 32 * k) & 7u);
 
     // ---- hand unassigned walks to idle slots
-    const unsigned idle0 = __ballot_sync(kFull, s0 == PS_IDLE), idle1 = __ballot_sync(kFull, s1 == PS_IDLE);
-    const int n_idle = __popc(idle0) + __popc(idle1);
+    unsigned idle[K];
+    int n_idle = 0;
+#pragma unroll
+    for (int k = 0; k < K; k++) { idle[k] = __ballot_sync(kFull, st[k] == PS_IDLE); n_idle += __popc(idle[k]); }
     if (n_idle && !drained) {
-      const int r0 = __popc(idle0 & lt), r1 = __popc(idle0) + __popc(idle1 & lt);
+      int rank[K], before = 0;
+#pragma unroll
+      for (int k = 0; k < K; k++) { rank[k] = before + __popc(idle[k] & lt); before += __popc(idle[k]); }
       int given = 0;
       while (given < n_idle) {
         if (q_next >= q_end) {
@@ -91,15 +100,13 @@ __global__ void __launch_bounds__(kBlock, 6) node2vec_pool_kernel(const Node2vec
           q_end = min(q_next + 32, n);
         }
         const int take = min((int)(q_end - q_next), n_idle - given);
-        if (s0 == PS_IDLE && r0 >= given && r0 < given + take) {
-          FLD(PF_I, lane) = (uint32_t)(q_next + (r0 - given));
-          FLD(PF_LS, lane) = PS_START;
-          s0 = PS_START;
-        }
-        if (s1 == PS_IDLE && r1 >= given && r1 < given + take) {
-          FLD(PF_I, lane + 32) = (uint32_t)(q_next + (r1 - given));
-          FLD(PF_LS, lane + 32) = PS_START;
-          s1 = PS_START;
+#pragma unroll
+        for (int k = 0; k < K; k++) {
+          if (st[k] == PS_IDLE && rank[k] >= given && rank[k] < given + take) {
+            FLD(PF_I, lane + 32 * k) = (uint32_t)(q_next + (rank[k] - given));
+            FLD(PF_LS, lane + 32 * k) = PS_START;
+            st[k] = PS_START;
+          }
         }
         q_next += take;
         given += take;
@@ -108,27 +115,34 @@ __global__ void __launch_bounds__(kBlock, 6) node2vec_pool_kernel(const Node2vec
     }
 
     // ---- pick the class most slots are in
-    const unsigned mA0 = __ballot_sync(kFull, s0 == PS_ATTEMPT), mA1 = __ballot_sync(kFull, s1 == PS_ATTEMPT);
-    const unsigned mH0 = __ballot_sync(kFull, s0 == PS_HASH), mH1 = __ballot_sync(kFull, s1 == PS_HASH);
-    const unsigned mR0 = __ballot_sync(kFull, s0 >= PS_START && s0 <= PS_ACCEPTED);
-    const unsigned mR1 = __ballot_sync(kFull, s1 >= PS_START && s1 <= PS_ACCEPTED);
-    const int nA = __popc(mA0) + __popc(mA1), nH = __popc(mH0) + __popc(mH1), nR = __popc(mR0) + __popc(mR1);
+    unsigned mA[K], mH[K], mR[K];
+    int nA = 0, nH = 0, nR = 0;
+#pragma unroll
+    for (int k = 0; k < K; k++) {
+      mA[k] = __ballot_sync(kFull, st[k] == PS_ATTEMPT);
+      mH[k] = __ballot_sync(kFull, st[k] == PS_HASH);
+      mR[k] = __ballot_sync(kFull, st[k] >= PS_START && st[k] <= PS_ACCEPTED);
+      nA += __popc(mA[k]); nH += __popc(mH[k]); nR += __popc(mR[k]);
+    }
     if (nA + nH + nR == 0) break;  // every slot idle: the queue is drained (idle slots are refilled above otherwise)
-    unsigned m0, m1;
     int cls;
-    if (nA >= nH && nA >= nR) { cls = PS_ATTEMPT; m0 = mA0; m1 = mA1; }
-    else if (nH >= nR) { cls = PS_HASH; m0 = mH0; m1 = mH1; }
-    else { cls = PS_ROW; m0 = mR0; m1 = mR1; }
-    {
-      const int k0 = __popc(m0 & lt), k1 = __popc(m0) + __popc(m1 & lt);
-      if (((m0 >> lane) & 1u) && k0 < 32) sel[warp][k0] = (uint8_t)lane;
-      if (((m1 >> lane) & 1u) && k1 < 32) sel[warp][k1] = (uint8_t)(lane + 32);
+    if (nA >= nH && nA >= nR) cls = PS_ATTEMPT;
+    else if (nH >= nR) cls = PS_HASH;
+    else cls = PS_ROW;
+    int cnt = 0;
+#pragma unroll
+    for (int k = 0; k < K; k++) {
+      const unsigned m = cls == PS_ATTEMPT ? mA[k] : (cls == PS_HASH ? mH[k] : mR[k]);
+      if ((m >> lane) & 1u) sel[warp][cnt + __popc(m & lt)] = (uint8_t)(lane + 32 * k);
+      cnt += __popc(m);
     }
     __syncwarp();
-    const int cnt = min(32, __popc(m0) + __popc(m1));
 
-    if (lane < cnt) {
-      const int s = sel[warp][lane];
+    // the slots of the class, 32 at a time (the choice above is paid once for all rounds); a last
+    // round that would fill less than half the warp is left for a later trip
+    for (int base = 0; base < cnt && (base == 0 || cnt - base >= 16); base += 32)
+    if (base + lane < cnt) {
+      const int s = sel[warp][base + lane];
       const int64_t i = (int64_t)FLD(PF_I, s);
       uint32_t ls = FLD(PF_LS, s);
       int32_t l = (int32_t)(ls >> 16);
