@@ -21,13 +21,11 @@ enum : int {
   PF_V,       // current node
   PF_RS,      // row start of v
   PF_DEG,     // degree of v (saturated at 2^31)
-  PF_INV,     // floor((2^32 - 1) / degree)
   PF_RET,     // index of the edge v -> t (kNoEdge / kUnknownEdge)
   PF_IN,      // index of the edge t -> v the walk arrived by
   PF_X,       // candidate
   PF_XREV,    // index of the edge x -> v, gathered with x
   PF_E,       // drawn edge
-  PF_LO,      // hash bucket being probed
   PF_A,       // attempt counter of this step
   PF_LS,      // state (bits 0-2) | buckets probed (bits 3-15) | step (bits 16-31)
   PF_COUNT
@@ -196,7 +194,6 @@ __global__ void __launch_bounds__(kBlock, 6) node2vec_pool_kernel(const Node2vec
             const uint32_t v_deg = deg > 0x7fffffffll ? 0x80000000u : (uint32_t)deg;
             FLD(PF_RS, s) = (uint32_t)rs;
             FLD(PF_DEG, s) = v_deg;
-            FLD(PF_INV, s) = 0xffffffffu / v_deg;
             FLD(PF_A, s) = 0;
             FLD(PF_LS, s) = ((uint32_t)l << 16) | PS_ATTEMPT;
           }
@@ -208,7 +205,8 @@ __global__ void __launch_bounds__(kBlock, 6) node2vec_pool_kernel(const Node2vec
       } else if (cls == PS_ATTEMPT) {
         // -------- draw candidates until one needs memory (or is decided), gather it, classify it
         const uint32_t t = FLD(PF_T, s), v = FLD(PF_V, s);
-        const uint32_t v_rs = FLD(PF_RS, s), v_deg = FLD(PF_DEG, s), v_inv = FLD(PF_INV, s);
+        const uint32_t v_rs = FLD(PF_RS, s), v_deg = FLD(PF_DEG, s);
+        const uint32_t v_inv = 0xffffffffu / v_deg;  // recomputed: a slot field less leaves the SM more L1
         const uint32_t ret_e = FLD(PF_RET, s);
         uint32_t a = FLD(PF_A, s);
         uint32_t e, acc = 0, x = 0;
@@ -259,10 +257,7 @@ __global__ void __launch_bounds__(kBlock, 6) node2vec_pool_kernel(const Node2vec
           else reject = true;
         }
         int next = PS_ATTEMPT;
-        if (probe) {
-          FLD(PF_LO, s) = (uint32_t)edge_bucket(edge_key((uint64_t)x, (uint64_t)t), P.edgeset_buckets);
-          next = PS_HASH;
-        }
+        if (probe) next = PS_HASH;
         if (reject) {
           a++;
           if (a >= P.max_attempts) {
@@ -279,17 +274,16 @@ __global__ void __launch_bounds__(kBlock, 6) node2vec_pool_kernel(const Node2vec
       } else {
         // -------- one 32-byte bucket of the edge hash set
         const uint32_t x = FLD(PF_X, s), t = FLD(PF_T, s);
-        uint32_t lo = FLD(PF_LO, s), hi = (ls >> 3) & 0x1fffu;
-        const void* addr = P.edgeset + (uint64_t)lo * kEdgeSlotsPerBucket;
-        const ulonglong2 h0 = ld16(addr, pol.stream), h1 = ld16((const char*)addr + 16, pol.stream);
+        uint32_t hi = (ls >> 3) & 0x1fffu;  // buckets probed so far: this trip reads bucket (home + hi) mod buckets
         const uint64_t key = edge_key((uint64_t)x, (uint64_t)t);
+        uint64_t lo = edge_bucket(key, P.edgeset_buckets) + hi;
+        while (lo >= P.edgeset_buckets) lo -= P.edgeset_buckets;
+        const void* addr = P.edgeset + lo * kEdgeSlotsPerBucket;
+        const ulonglong2 h0 = ld16(addr, pol.stream), h1 = ld16((const char*)addr + 16, pol.stream);
         bool accept = false, reject = false;
         if (h0.x == key || h0.y == key || h1.x == key || h1.y == key) accept = true;
         else if (h0.x == kEdgeEmpty || h0.y == kEdgeEmpty || h1.x == kEdgeEmpty || h1.y == kEdgeEmpty) reject = true;
-        else {
-          if (++lo == (uint32_t)P.edgeset_buckets) lo = 0;
-          if (++hi >= (uint32_t)kEdgeMaxProbe) { raise_flag(P.flags, WALK_B200_FLAG_EDGESET_FULL); reject = true; }
-        }
+        else if (++hi >= (uint32_t)kEdgeMaxProbe) { raise_flag(P.flags, WALK_B200_FLAG_EDGESET_FULL); reject = true; }
         int next = PS_HASH;
         if (reject) {
           uint32_t a = FLD(PF_A, s) + 1;
@@ -304,7 +298,6 @@ __global__ void __launch_bounds__(kBlock, 6) node2vec_pool_kernel(const Node2vec
           FLD(PF_A, s) = a;
         }
         if (accept) { next = PS_ACCEPTED; hi = 0; }
-        FLD(PF_LO, s) = lo;
         FLD(PF_LS, s) = ((uint32_t)l << 16) | (hi << 3) | (uint32_t)next;
       }
     }
