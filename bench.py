@@ -46,8 +46,8 @@ RMAT = dict(a=0.57, b=0.19, c=0.19, d=0.05)
 # profiles/: measured on the scale-20 case of each workload; the full-size figures are that measurement
 # scaled by the number of gathers issued (traffic is proportional to gathers; see the profile notes).
 NCU_TRAFFIC = {
-    "node2vec_rmat20": (18.16e9, "ncu, measured"),
-    "node2vec_rmat24": (18.16e9 * 14.90, "ncu on node2vec_rmat20 scaled by gathers issued (x14.90)"),
+    "node2vec_rmat20": (19.60e9, "ncu, measured"),
+    "node2vec_rmat24": (19.60e9 * 14.90, "ncu on node2vec_rmat20 scaled by gathers issued (x14.90)"),
     "uniform_rmat20": (4.70e9, "ncu, measured"),
     "uniform_rmat22": (4.70e9 * 3.72, "ncu on uniform_rmat20 scaled by gathers issued (x3.72)"),
 }
@@ -421,7 +421,7 @@ def run_ours(args, wl):
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_source": f"of {peak_kind}",
                 "traffic": NCU_TRAFFIC.get(args.workload, (None, None))[0] if world == 1 else None,
-                "traffic_source": NCU_TRAFFIC.get(args.workload, (None, None))[1], "kernel": "node2vec_walk_kernel" if
+                "traffic_source": NCU_TRAFFIC.get(args.workload, (None, None))[1], "kernel": "node2vec_pool_kernel (node2vec_walk_kernel where the pooled form does not apply)" if
                 wl["kind"] == "node2vec" else "uniform_walk_staged_kernel", "kernel_ms": kernel_ms,
                 "algorithmic_bytes_per_launch": alg_bytes, "gathered_bytes_per_launch": gathered_bytes,
                 "gathered_gbs": allsum(gathered_bytes / (kernel_ms * 1e-3) / 1e9) / world,
