@@ -363,7 +363,12 @@ int walk_b200_negative_draw(uint64_t seed, uint64_t row, uint32_t k, int64_t num
  */
 int walk_b200_gather_probe(size_t array_bytes, int32_t iters, double* gathers_per_second);
 
-/* Kernel variant selection for experiments ("uniform_variant", "n2v_member", "l2_hints", ...); unknown keys fail. */
+/* Kernel variant and transport selection; unknown keys fail. None of them changes a result.
+ *   uniform_variant, uniform_fused, l2_hints, l2_fetch_granularity, use_rowdesc
+ *   n2v_idx, n2v_member, n2v_rev, n2v_pool (0 per-lane kernel, 1 pooled kernel where it wins, 2 always),
+ *   n2v_batch_lanes, n2v_batch_trips, n2v_draw_loop, n2v_blocks_per_sm
+ *   host_slab_mb, host_narrow (int32 on the bus), host_threads (widening threads, 0 = min(16, cores)),
+ *   host_single_launch (node2vec host entry as one launch), host_resident_mb (its device-memory limit) */
 int walk_b200_set_tuning(const char* key, int32_t value);
 int walk_b200_get_tuning(const char* key, int32_t* value);
 
