@@ -1044,6 +1044,12 @@ int run_host_n2v_single(walk_b200_graph* g, const walk_b200_csr& csr, const int6
   const size_t need = (size_t)n * row32 + (want_e ? (size_t)n * L * 4 : 0);
   if (need > ((size_t)g_tuning.host_resident_mb.load() << 20)) return kNoHostKernel;
   if (g_tuning.n2v_idx.load() == 1) return kNoHostKernel;
+  {  // the matrices must fit what the device has left (buffers kept from earlier calls count as free)
+    size_t free_b = 0, total_b = 0;
+    CUDA_TRY(cudaMemGetInfo(&free_b, &total_b));
+    const size_t kept = g->cap_all + g->cap_eall + g->cap_start_all;
+    if (need + (size_t)n * 8 + ((size_t)64 << 20) > free_b + kept) return kNoHostKernel;
+  }
 
   // slab: the largest power of two of rows whose int32 copy is at most an eighth of the slab tuning
   // (small slabs keep the staging copy cache-warm for the widening threads and shorten the exposed tail)
