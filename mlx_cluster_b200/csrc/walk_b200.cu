@@ -1078,6 +1078,10 @@ int run_host_n2v_single(walk_b200_graph* g, const walk_b200_csr& csr, const int6
   CUDA_TRY(cudaHostGetDevicePointer((void**)&d_slab_flags, g->h_slab_flags, 0));
 
   cudaStream_t work = g->streams[0], copy = g->streams[1];
+  // idle after a normal call; after a call that returned early with an error they may not be, and a
+  // launch still running must not set flags of this call
+  CUDA_TRY(cudaStreamSynchronize(work));
+  CUDA_TRY(cudaStreamSynchronize(copy));
   volatile uint32_t* flags = g->h_slab_flags;
   for (int64_t k = 0; k < slabs; k++) flags[k] = 0;
   CUDA_TRY(cudaMemsetAsync(g->d_flags, 0, sizeof(uint32_t), work));
