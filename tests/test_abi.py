@@ -70,6 +70,27 @@ def test_negative_draw_replays_the_documented_stream(walklib):
         _lib.negative_draw(1, 2, 3, 2**32 + 1)
 
 
+def test_csr_build_scratch_size_and_argument_checks(walklib):
+    """Host arithmetic of the device CSR builder: 8 bytes per slot (a directed edge before duplicates
+    are dropped) plus per-node arrays; limits and unknown option bits are refused."""
+    def need(m, n, options):
+        v = C.c_uint64(0)
+        _lib.check(walklib.walk_b200_csr_build_scratch_bytes(m, n, options, C.byref(v)))
+        return int(v.value)
+    sym = _lib.BUILD_SYMMETRIZE
+    m, n = 1_000_000, 50_000
+    one, two = need(m, n, 0), need(m, n, sym)
+    assert 8 * m <= one <= 8 * m + 16 * n + (1 << 16)
+    assert 16 * m <= two <= 16 * m + 16 * n + (1 << 16) and two > one
+    assert need(m, n, sym | _lib.BUILD_DROP_SELF_LOOPS | _lib.BUILD_DEDUPE) == two
+    assert need(0, 0, 0) > 0 and need(10, 3, sym) % 256 == 0
+    for bad in ((-1, 5, 0), (5, -1, 0), (5, 5, 0x10), (1 << 31, 5, 0), (5, 1 << 31, 0)):
+        with pytest.raises(_lib.WalkError):
+            need(*bad)
+    with pytest.raises(_lib.WalkError):
+        _lib.check(walklib.walk_b200_csr_build_scratch_bytes(5, 5, 0, None))
+
+
 def test_thresholds_and_cuts_match_oracle(walklib):
     for p, q in [(1, 1), (0.5, 2), (4, 0.25), (0.25, 4), (1, 2), (1, 3), (0.7, 1.3), (3.3, 0.011), (100.0, 100.0)]:
         prob, cuts = _lib.node2vec_thresholds(p, q)
