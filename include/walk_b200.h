@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define WALK_B200_ABI_VERSION 7
+#define WALK_B200_ABI_VERSION 8
 
 /* ---- return codes ---- */
 #define WALK_B200_OK 0
@@ -101,6 +101,9 @@ int walk_b200_abi_version(void);
 const char* walk_b200_last_error(void);
 /* Number of kernels this library has launched in this process (all threads). */
 uint64_t walk_b200_launch_count(void);
+/* Name of the kernel the calling thread launched last through this library ("" before the first launch),
+ * e.g. "node2vec_pool_kernel": lets a host check which variant a call selected. */
+const char* walk_b200_last_kernel(void);
 
 /*
  * Uniform CSR walk. Replaces RandomWalk::eval_cpu (random_walks/RandomWalk.cpp:18-62),
@@ -268,6 +271,9 @@ int walk_b200_csr_build(const int64_t* src, const int64_t* dst, int64_t num_inpu
  */
 typedef struct walk_b200_graph walk_b200_graph;
 
+/* validate: 0 = trust the arrays; 1 = run walk_b200_csr_validate with the sorted-rows check on the uploaded graph
+ * and fail with WALK_B200_ERR_CSR_INVALID on any finding (what node2vec without the edge hash set needs: its
+ * membership test is then a binary search); 2 = the same without the sorted-rows check. */
 int walk_b200_graph_create(const int64_t* h_rowptr, const int64_t* h_col, int64_t num_nodes,
                            int64_t num_edges, uint32_t csr_flags, int32_t validate,
                            walk_b200_graph** out);
@@ -335,7 +341,8 @@ int walk_b200_uniform_walk_noalloc(const int64_t* rowptr, const int64_t* col, in
  * in the reference, whose README lists further algorithms as future work, README.md:65-69): all runs of
  * context_size consecutive nodes of every walk, windows[(w * nwin + j) * cs + k] = walks[w, j + k] with
  * nwin = walk_length + 2 - context_size; column 0 is the centre node, the rest its skip-gram context.
- * windows is int64 [num_walks * nwin, context_size], device, caller-allocated.
+ * windows is int64 [num_walks * nwin, context_size], device, caller-allocated; like walks it only needs the
+ * 8-byte alignment of its element type (a view that starts at an odd element of a larger buffer is fine).
  */
 int walk_b200_context_windows(const int64_t* walks, int64_t num_walks, int32_t walk_length,
                               int32_t context_size, int64_t* windows, void* stream);
@@ -362,11 +369,23 @@ int walk_b200_negative_draw(uint64_t seed, uint64_t row, uint32_t k, int64_t num
  * whether a miss moves 64 or 128 bytes. No counterpart in the reference.
  */
 int walk_b200_gather_probe(size_t array_bytes, int32_t iters, double* gathers_per_second);
+/* The same probe with its shape exposed, to tell a limit of the memory system from a limit of the
+ * probe: `chains` (1, 2 or 4) independent chains per thread, i.e. that many gathers in flight per
+ * thread; `gather_bytes` (8, 16 or 32) per gather; `fetch_bytes` 64 (the L2 fetches half a line per
+ * miss, as the walks ask for) or 128 (the part's default, a whole line); `threads_per_sm` 0 for 2^22
+ * threads in several full waves, else one wave of that many resident threads per SM (a multiple of 256
+ * up to 2048). The plain probe above is (1, 8, 64, 0). */
+int walk_b200_gather_probe_ex(size_t array_bytes, int32_t iters, int32_t chains, int32_t gather_bytes,
+                              int32_t fetch_bytes, int32_t threads_per_sm, double* gathers_per_second);
 
-/* Kernel variant and transport selection; unknown keys fail. None of them changes a result.
+/* Kernel variant and transport selection; unknown keys fail. None of them changes a result (but see n2v_max_attempts).
  *   uniform_variant, uniform_fused, l2_hints, l2_fetch_granularity, use_rowdesc
  *   n2v_idx, n2v_member, n2v_rev, n2v_pool (0 per-lane kernel, 1 pooled kernel where it wins, 2 always),
- *   n2v_batch_lanes, n2v_batch_trips, n2v_draw_loop, n2v_blocks_per_sm
+ *   n2v_batch_lanes, n2v_batch_trips, n2v_draw_loop, n2v_blocks_per_sm,
+ *   n2v_drain (pooled kernel once the walk queue is dry: bit 0 packs a block's remaining walks into few warps,
+ *   bit 1 lets a warp with at most 32 of them advance every one each trip; 0 = neither), n2v_drain_trips,
+ *   n2v_max_attempts (rejections after which a step gives up, at most WALK_B200_MAX_ATTEMPTS: the one key that
+ *   can change a result, and only for steps that reach the cap, which raise WALK_B200_FLAG_ATTEMPT_CAP)
  *   host_slab_mb, host_narrow (int32 on the bus), host_threads (widening threads, 0 = min(16, cores)),
  *   host_single_launch (node2vec host entry as one launch), host_resident_mb (its device-memory limit) */
 int walk_b200_set_tuning(const char* key, int32_t value);

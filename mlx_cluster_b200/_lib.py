@@ -21,7 +21,7 @@ COUNTER_NAMES = ("loads", "attempts", "membership", "probes",
 
 # every symbol include/walk_b200.h declares
 EXPORTS = (
-    "walk_b200_abi_version", "walk_b200_last_error", "walk_b200_launch_count",
+    "walk_b200_abi_version", "walk_b200_last_error", "walk_b200_launch_count", "walk_b200_last_kernel",
     "walk_b200_uniform_walk", "walk_b200_uniform_walk_philox", "walk_b200_uniform_draw",
     "walk_b200_uniform_draws", "walk_b200_node2vec_walk", "walk_b200_rowdesc_pack",
     "walk_b200_csr_validate", "walk_b200_edgeset_buckets", "walk_b200_edgeset_build", "walk_b200_revpos_build", "walk_b200_colrev_build", "walk_b200_fused_build", "walk_b200_philox4x32_10", "walk_b200_node2vec_draw",
@@ -30,7 +30,7 @@ EXPORTS = (
     "walk_b200_graph_device_bytes", "walk_b200_uniform_walk_host", "walk_b200_node2vec_walk_host",
     "walk_b200_l2_window_set", "walk_b200_l2_window_clear",
     "walk_b200_set_tuning", "walk_b200_get_tuning",
-    "walk_b200_uniform_walk_noalloc", "walk_b200_gather_probe", "walk_b200_context_windows",
+    "walk_b200_uniform_walk_noalloc", "walk_b200_gather_probe", "walk_b200_gather_probe_ex", "walk_b200_context_windows",
     "walk_b200_csr_build_scratch_bytes", "walk_b200_csr_build",
     "walk_b200_negative_walks", "walk_b200_negative_draw",
 )
@@ -67,6 +67,7 @@ def lib():
     L.walk_b200_abi_version.restype = C.c_int
     L.walk_b200_last_error.restype = C.c_char_p
     L.walk_b200_launch_count.restype = u64
+    L.walk_b200_last_kernel.restype = C.c_char_p
     L.walk_b200_uniform_walk.argtypes = [C.POINTER(Csr), vp, vp, i64, i32, vp, vp, vp, vp]
     L.walk_b200_uniform_walk_philox.argtypes = [C.POINTER(Csr), vp, i64, i32, u64, u64, u64, vp, vp, vp, vp]
     L.walk_b200_uniform_draw.argtypes = [u64, u64, u32, C.POINTER(C.c_float)]
@@ -103,6 +104,7 @@ def lib():
     L.walk_b200_csr_build_scratch_bytes.argtypes = [i64, i64, C.c_uint32, C.POINTER(C.c_uint64)]
     L.walk_b200_csr_build.argtypes = [vp, vp, i64, i64, C.c_uint32, vp, C.c_uint64, vp, vp, vp, vp]
     L.walk_b200_gather_probe.argtypes = [C.c_size_t, i32, C.POINTER(dbl)]
+    L.walk_b200_gather_probe_ex.argtypes = [C.c_size_t, i32, i32, i32, i32, i32, C.POINTER(dbl)]
     L.walk_b200_set_tuning.argtypes = [C.c_char_p, i32]
     L.walk_b200_get_tuning.argtypes = [C.c_char_p, C.POINTER(i32)]
     for name in EXPORTS:  # AttributeError here = the built library is older than the header
@@ -118,6 +120,11 @@ def check(rc: int) -> None:
 
 def launch_count() -> int:
     return int(lib().walk_b200_launch_count())
+
+
+def last_kernel() -> str:
+    """Name of the kernel this thread launched last through the library."""
+    return lib().walk_b200_last_kernel().decode()
 
 
 def set_tuning(key: str, value: int) -> None:
@@ -160,10 +167,13 @@ def node2vec_thresholds(p: float, q: float):
     return tuple(prob), tuple(cuts)
 
 
-def gather_probe(array_bytes: int = 2 << 30, iters: int = 32) -> float:
-    """Dependent random 8-byte gathers per second this device sustains out of DRAM."""
+def gather_probe(array_bytes: int = 2 << 30, iters: int = 32, *, chains: int = 1, gather_bytes: int = 8,
+                 fetch_bytes: int = 64, threads_per_sm: int = 0) -> float:
+    """Dependent random gathers per second this device sustains out of DRAM (``chains`` of them in
+    flight per thread, ``gather_bytes`` each, the L2 fetching ``fetch_bytes`` per miss)."""
     r = C.c_double(0.0)
-    check(lib().walk_b200_gather_probe(array_bytes, iters, C.byref(r)))
+    check(lib().walk_b200_gather_probe_ex(array_bytes, iters, chains, gather_bytes, fetch_bytes, threads_per_sm,
+                                          C.byref(r)))
     return float(r.value)
 
 

@@ -27,6 +27,7 @@ namespace {
 using namespace walk_b200;
 
 thread_local std::string g_last_error;
+thread_local const char* g_last_kernel = "";  // name of the kernel this thread launched last (string literals only)
 std::atomic<uint64_t> g_launches{0};
 
 int fail(int code, const char* fmt, ...) {
@@ -51,6 +52,7 @@ int check_launch(const char* what) {
   if (err != cudaSuccess)
     return fail(WALK_B200_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(err));
   g_launches.fetch_add(1, std::memory_order_relaxed);
+  g_last_kernel = what;
   return WALK_B200_OK;
 }
 
@@ -68,6 +70,10 @@ struct Tuning {
   std::atomic<int32_t> n2v_rev{1};          // 1 auto (reverse positions when they pay), 0 never, 2 whenever available
   std::atomic<int32_t> n2v_pool{1};         // 1: pooled kernel (walk state in shared memory, one state class per trip)
   std::atomic<int32_t> n2v_blocks_per_sm{0};  // 0 = what the occupancy calculator allows
+  std::atomic<int32_t> n2v_drain{3};        // pooled kernel, once the queue is dry: bit 0 pack the block's live slots
+                                            // into few warps, bit 1 warps with <= 32 live slots serve all of them
+  std::atomic<int32_t> n2v_drain_trips{8};  // ... trips between two packing rounds
+  std::atomic<int32_t> n2v_max_attempts{(int32_t)WALK_B200_MAX_ATTEMPTS};  // rejections after which a step gives up
   std::atomic<int32_t> l2_hints{3};         // bit 0: evict-last row bounds, bit 1: evict-first streams
   std::atomic<int32_t> l2_fetch_granularity{0};  // set only through walk_b200_set_tuning (applies the CUDA limit)
   std::atomic<int32_t> host_slab_mb{256};   // walk-matrix bytes per pipeline slab of the host entry points
@@ -91,6 +97,9 @@ std::atomic<int32_t>* tuning_slot(const char* key) {
   if (!strcmp(key, "n2v_batch_trips")) return &g_tuning.n2v_batch_trips;
   if (!strcmp(key, "n2v_draw_loop")) return &g_tuning.n2v_draw_loop;
   if (!strcmp(key, "n2v_blocks_per_sm")) return &g_tuning.n2v_blocks_per_sm;
+  if (!strcmp(key, "n2v_drain")) return &g_tuning.n2v_drain;
+  if (!strcmp(key, "n2v_drain_trips")) return &g_tuning.n2v_drain_trips;
+  if (!strcmp(key, "n2v_max_attempts")) return &g_tuning.n2v_max_attempts;
   if (!strcmp(key, "l2_hints")) return &g_tuning.l2_hints;
   if (!strcmp(key, "l2_fetch_granularity")) return &g_tuning.l2_fetch_granularity;
   if (!strcmp(key, "host_slab_mb")) return &g_tuning.host_slab_mb;
@@ -256,7 +265,7 @@ int next_queue_slot(unsigned long long** out) {
 
 // Persistent launch: as many blocks as fit on the device at once (or fewer, if the batch is small).
 template <typename K>
-int launch_n2v_kernel(K kernel, const Node2vecParams& P0, cudaStream_t s) {
+int launch_n2v_kernel(K kernel, const Node2vecParams& P0, cudaStream_t s, const char* name = "node2vec_walk_kernel") {
   Node2vecParams P = P0;
   if (int rc = next_queue_slot(&P.queue)) return rc;
   CUDA_TRY(cudaMemsetAsync(P.queue, 0, sizeof(unsigned long long), s));
@@ -272,7 +281,7 @@ int launch_n2v_kernel(K kernel, const Node2vecParams& P0, cudaStream_t s) {
   if (grid > needed) grid = needed;
   if (grid < 1) grid = 1;
   kernel<<<(unsigned)grid, kBlock, 0, s>>>(P);
-  return check_launch("node2vec_walk_kernel");
+  return check_launch(name);
 }
 
 template <typename idx_t, int MEMBER, bool USE_DESC>
@@ -319,7 +328,7 @@ bool pool_applies(const Node2vecParams& P, int member) {
   const int mode = g_tuning.n2v_pool.load();
   return mode != 0 && (mode == 2 || rev_pays(P)) && member == MEMBER_HASH && P.colrev && P.desc && !P.counters &&
          P.num_nodes <= 0x7fffffffll && P.num_edges < 0xfffffffell && P.edgeset_buckets < 0xffffffffull &&
-         P.num_walks < 0xffffffffll && P.walk_length < 65536 && g_tuning.n2v_idx.load() != 1 &&
+         P.num_walks < 0xffffff00ll && P.walk_length < 65536 && g_tuning.n2v_idx.load() != 1 &&
          g_tuning.n2v_rev.load() != 0;
 }
 
@@ -327,8 +336,8 @@ int launch_n2v(const Node2vecParams& P, bool sym, cudaStream_t s) {
   int member = sym ? MEMBER_SEARCH_PREV : MEMBER_SEARCH_CAND;
   if (P.edgeset && P.edgeset_buckets > 0 && g_tuning.n2v_member.load() != 1) member = MEMBER_HASH;
   if (pool_applies(P, member)) {
-    if (P.e_out) return launch_n2v_kernel(node2vec_pool_kernel<true, false>, P, s);
-    return launch_n2v_kernel(node2vec_pool_kernel<false, false>, P, s);
+    if (P.e_out) return launch_n2v_kernel(node2vec_pool_kernel<true, false>, P, s, "node2vec_pool_kernel");
+    return launch_n2v_kernel(node2vec_pool_kernel<false, false>, P, s, "node2vec_pool_kernel");
   }
   const bool fits32 = P.num_nodes <= 0x7fffffffll && P.num_edges <= 0xffffffffll;
   if (member == MEMBER_HASH && P.colrev && P.desc && fits32 && P.num_edges < 0xfffffffell &&
@@ -357,8 +366,8 @@ int launch_n2v_host(const Node2vecParams& P, bool sym, cudaStream_t s) {
   int member = sym ? MEMBER_SEARCH_PREV : MEMBER_SEARCH_CAND;
   if (P.edgeset && P.edgeset_buckets > 0 && g_tuning.n2v_member.load() != 1) member = MEMBER_HASH;
   if (pool_applies(P, member)) {
-    if (e) return launch_n2v_kernel(node2vec_pool_kernel<true, true>, P, s);
-    return launch_n2v_kernel(node2vec_pool_kernel<false, true>, P, s);
+    if (e) return launch_n2v_kernel(node2vec_pool_kernel<true, true>, P, s, "node2vec_pool_kernel");
+    return launch_n2v_kernel(node2vec_pool_kernel<false, true>, P, s, "node2vec_pool_kernel");
   }
   if (member == MEMBER_HASH && P.colrev && rev_pays(P)) {
     if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, true, false, true, true>, P, s);
@@ -395,7 +404,13 @@ int prepare_n2v(const walk_b200_csr* g, const int64_t* start, int64_t num_walks,
   P.key0 = (uint32_t)seed; P.key1 = (uint32_t)(seed >> 32);
   P.walk_index_base = walk_index_base;
   P.walk_index_stride = walk_index_stride ? walk_index_stride : 1;
-  P.max_attempts = WALK_B200_MAX_ATTEMPTS;
+  {
+    const int32_t cap = g_tuning.n2v_max_attempts.load();
+    P.max_attempts = cap < 1 ? 1u : (uint32_t)cap > WALK_B200_MAX_ATTEMPTS ? WALK_B200_MAX_ATTEMPTS : (uint32_t)cap;
+  }
+  P.drain = g_tuning.n2v_drain.load() & 3;
+  P.drain_trips = g_tuning.n2v_drain_trips.load();
+  if (P.drain_trips < 1) P.drain_trips = 1;
   P.batch_lanes = g_tuning.n2v_batch_lanes.load();
   P.batch_trips = g_tuning.n2v_batch_trips.load();
   if (P.batch_lanes < 1) P.batch_lanes = 1;
@@ -457,6 +472,8 @@ int walk_b200_abi_version(void) { return WALK_B200_ABI_VERSION; }
 const char* walk_b200_last_error(void) { return g_last_error.c_str(); }
 
 uint64_t walk_b200_launch_count(void) { return g_launches.load(); }
+
+const char* walk_b200_last_kernel(void) { return g_last_kernel; }
 
 int walk_b200_set_tuning(const char* key, int32_t value) {
   auto* slot = tuning_slot(key);
@@ -703,12 +720,17 @@ int walk_b200_context_windows(const int64_t* walks, int64_t num_walks, int32_t w
   const uint64_t magic = (1ull << 32) / (uint64_t)context_size + 1;
   const bool fast = magic <= 0xffffffffull &&
                     (uint64_t)per_walk * (magic * (uint64_t)context_size - (1ull << 32)) < (1ull << 32);
+  if ((reinterpret_cast<uintptr_t>(walks) & 7) != 0 || (reinterpret_cast<uintptr_t>(windows) & 7) != 0)
+    return fail(WALK_B200_ERR_INVALID_ARG, "walks and windows must be 8-byte aligned");
+  // the kernel stores pairs of elements with one 16-byte store where the pair starts on a 16-byte boundary;
+  // which pairs do depends on where the caller's matrix starts (a view that begins at an odd element is fine)
+  const bool base_aligned = (reinterpret_cast<uintptr_t>(windows) & 15) == 0;
   if (fast)
     context_windows_kernel<true><<<grid, kBlock, 0, (cudaStream_t)stream>>>(
-        walks, num_walks, walk_length + 1, context_size, (uint32_t)magic, (int32_t)per_walk, windows);
+        walks, num_walks, walk_length + 1, context_size, (uint32_t)magic, (int32_t)per_walk, windows, base_aligned);
   else
     context_windows_kernel<false><<<grid, kBlock, 0, (cudaStream_t)stream>>>(
-        walks, num_walks, walk_length + 1, context_size, 0u, (int32_t)per_walk, windows);
+        walks, num_walks, walk_length + 1, context_size, 0u, (int32_t)per_walk, windows, base_aligned);
   return check_launch("context_windows_kernel");
 }
 
@@ -740,16 +762,44 @@ int walk_b200_negative_draw(uint64_t seed, uint64_t row, uint32_t k, int64_t num
   return WALK_B200_OK;
 }
 
+}  // extern "C"
+
 // ---- device probe -------------------------------------------------------------------
-int walk_b200_gather_probe(size_t array_bytes, int32_t iters, double* gathers_per_second) {
+namespace {
+typedef void (*ProbeKernel)(const int64_t*, uint64_t, int, int64_t*);
+
+template <int CHAINS>
+ProbeKernel probe_kernel_for(int bytes, bool fetch64) {
+  if (bytes == 8) return fetch64 ? gather_probe_kernel<CHAINS, 8, true> : gather_probe_kernel<CHAINS, 8, false>;
+  if (bytes == 16) return fetch64 ? gather_probe_kernel<CHAINS, 16, true> : gather_probe_kernel<CHAINS, 16, false>;
+  return fetch64 ? gather_probe_kernel<CHAINS, 32, true> : gather_probe_kernel<CHAINS, 32, false>;
+}
+}  // namespace
+
+extern "C" {
+
+int walk_b200_gather_probe_ex(size_t array_bytes, int32_t iters, int32_t chains, int32_t gather_bytes,
+                              int32_t fetch_bytes, int32_t threads_per_sm, double* gathers_per_second) {
   if (!gathers_per_second || iters < 1 || array_bytes < (1u << 20))
     return fail(WALK_B200_ERR_INVALID_ARG, "gather probe needs an array of at least 1 MiB and iters >= 1");
+  if (chains != 1 && chains != 2 && chains != 4)
+    return fail(WALK_B200_ERR_INVALID_ARG, "gather probe: chains must be 1, 2 or 4");
+  if (gather_bytes != 8 && gather_bytes != 16 && gather_bytes != 32)
+    return fail(WALK_B200_ERR_INVALID_ARG, "gather probe: gather_bytes must be 8, 16 or 32");
+  if (fetch_bytes != 64 && fetch_bytes != 128)
+    return fail(WALK_B200_ERR_INVALID_ARG, "gather probe: fetch_bytes must be 64 or 128");
+  if (threads_per_sm != 0 && (threads_per_sm < kBlock || threads_per_sm > 2048 || threads_per_sm % kBlock))
+    return fail(WALK_B200_ERR_INVALID_ARG, "gather probe: threads_per_sm must be 0 or a multiple of %d up to 2048", kBlock);
   *gathers_per_second = 0.0;
+  const ProbeKernel kernel = chains == 1 ? probe_kernel_for<1>(gather_bytes, fetch_bytes == 64)
+                           : chains == 2 ? probe_kernel_for<2>(gather_bytes, fetch_bytes == 64)
+                                         : probe_kernel_for<4>(gather_bytes, fetch_bytes == 64);
   int64_t* data = nullptr;
   int64_t* sink = nullptr;
   cudaEvent_t a = nullptr, b = nullptr;
-  const uint64_t n = array_bytes / 8;
-  const int threads = 1 << 22;
+  const uint64_t n = array_bytes / 32 * 4;  // whole 32-byte pieces, so that every gather width divides the array
+  // threads_per_sm = 0: 2^22 threads, several waves of full occupancy; otherwise one wave of that many per SM
+  const int64_t threads = threads_per_sm ? (int64_t)sm_count() * threads_per_sm : (int64_t)1 << 22;
   int rc = WALK_B200_OK;
   auto cleanup = [&]() {
     if (a) cudaEventDestroy(a);
@@ -771,10 +821,11 @@ int walk_b200_gather_probe(size_t array_bytes, int32_t iters, double* gathers_pe
   P_TRY(cudaMemset(data, 0, n * 8));
   P_TRY(cudaEventCreate(&a));
   P_TRY(cudaEventCreate(&b));
-  gather_probe_kernel<<<threads / kBlock, kBlock>>>(data, n, iters, sink);  // warm-up
+  const unsigned grid = (unsigned)(threads / kBlock);
+  kernel<<<grid, kBlock>>>(data, n, iters, sink);  // warm-up
   if ((rc = check_launch("gather_probe_kernel"))) { cleanup(); return rc; }
   P_TRY(cudaEventRecord(a));
-  gather_probe_kernel<<<threads / kBlock, kBlock>>>(data, n, iters, sink);
+  kernel<<<grid, kBlock>>>(data, n, iters, sink);
   if ((rc = check_launch("gather_probe_kernel"))) { cleanup(); return rc; }
   P_TRY(cudaEventRecord(b));
   P_TRY(cudaEventSynchronize(b));
@@ -782,8 +833,12 @@ int walk_b200_gather_probe(size_t array_bytes, int32_t iters, double* gathers_pe
   P_TRY(cudaEventElapsedTime(&ms, a, b));
 #undef P_TRY
   cleanup();
-  if (ms > 0.f) *gathers_per_second = (double)threads * iters / (ms * 1e-3);
+  if (ms > 0.f) *gathers_per_second = (double)threads * iters * chains / (ms * 1e-3);
   return WALK_B200_OK;
+}
+
+int walk_b200_gather_probe(size_t array_bytes, int32_t iters, double* gathers_per_second) {
+  return walk_b200_gather_probe_ex(array_bytes, iters, 1, 8, 64, 0, gathers_per_second);
 }
 
 // ---- L2 residency hint -------------------------------------------------------------
@@ -1293,7 +1348,7 @@ int walk_b200_graph_create(const int64_t* h_rowptr, const int64_t* h_col, int64_
   if (validate) {
     walk_b200_csr csr{};
     csr.rowptr = g->d_rowptr; csr.col = g->d_col; csr.num_nodes = num_nodes; csr.num_edges = num_edges;
-    if (int rc = walk_b200_csr_validate(&csr, nullptr, 0, 1, g->d_flags, s)) return bail(rc);
+    if (int rc = walk_b200_csr_validate(&csr, nullptr, 0, validate == 2 ? 0 : 1, g->d_flags, s)) return bail(rc);
     G_TRY(cudaMemcpyAsync(&f, g->d_flags, 4, cudaMemcpyDeviceToHost, s));
     G_TRY(cudaStreamSynchronize(s));
     if (f) { flags_to_status(f); return bail(fail(WALK_B200_ERR_CSR_INVALID, "graph failed validation: %s", std::string(g_last_error).c_str())); }

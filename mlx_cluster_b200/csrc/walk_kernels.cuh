@@ -111,18 +111,45 @@ __device__ __forceinline__ uint64_t splitmix64(uint64_t z) {
   return z;
 }
 
+// CHAINS independent chains per thread (that many gathers in flight per thread), BYTES per gather
+// (8, 16 or 32, naturally aligned), and the amount the L2 fetches from DRAM on a miss (64-byte
+// prefetch size as the walks use, or the part's default of a whole 128-byte line).
+template <int CHAINS, int BYTES, bool FETCH64>
 __global__ void __launch_bounds__(kBlock) gather_probe_kernel(const int64_t* __restrict__ data,
                                                               uint64_t num_elems, int iters,
                                                               int64_t* sink) {
-  const L2Policy pol = make_policies(0);
+  static_assert(BYTES == 8 || BYTES == 16 || BYTES == 32, "gather width");
+  constexpr int kWords = BYTES / 8;
   const uint64_t tid = (uint64_t)blockIdx.x * kBlock + threadIdx.x;
-  uint64_t idx = splitmix64(tid + 1);
-  int64_t acc = 0;
+  uint64_t idx[CHAINS];
+  int64_t acc[CHAINS];
+#pragma unroll
+  for (int c = 0; c < CHAINS; c++) { idx[c] = splitmix64(tid * CHAINS + c + 1); acc[c] = 0; }
+  const uint64_t slots = num_elems / kWords;
   for (int i = 0; i < iters; i++) {
-    idx = splitmix64(idx + (uint64_t)acc);
-    acc += ld8(data + __umul64hi(idx, num_elems), pol.normal);
+#pragma unroll
+    for (int c = 0; c < CHAINS; c++) {
+      idx[c] = splitmix64(idx[c] + (uint64_t)acc[c]);
+      const int64_t* addr = data + __umul64hi(idx[c], slots) * kWords;
+      int64_t a = 0, b = 0, d = 0, e = 0;
+      if (BYTES == 8) {
+        if (FETCH64) asm volatile("ld.global.nc.L2::64B.b64 %0, [%1];" : "=l"(a) : "l"(addr));
+        else asm volatile("ld.global.nc.b64 %0, [%1];" : "=l"(a) : "l"(addr));
+      } else {
+        if (FETCH64) asm volatile("ld.global.nc.L2::64B.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(addr));
+        else asm volatile("ld.global.nc.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(addr));
+        if (BYTES == 32) {
+          if (FETCH64) asm volatile("ld.global.nc.L2::64B.v2.b64 {%0, %1}, [%2];" : "=l"(d), "=l"(e) : "l"(addr + 2));
+          else asm volatile("ld.global.nc.v2.b64 {%0, %1}, [%2];" : "=l"(d), "=l"(e) : "l"(addr + 2));
+        }
+      }
+      acc[c] += a + b + d + e;
+    }
   }
-  if (acc == 0x7fffffffffffffffll) *sink = acc;  // never true on a zeroed array; keeps the chain alive
+  int64_t total = 0;
+#pragma unroll
+  for (int c = 0; c < CHAINS; c++) total += acc[c];
+  if (total == 0x7fffffffffffffffll) *sink = total;  // never true on a zeroed array; keeps the chains alive
 }
 
 // ---------------------------------------------------------------------------------
@@ -266,6 +293,10 @@ __device__ __forceinline__ int64_t uniform_step(const UniformParams& P, const L2
   int64_t e = rs + __float2ll_rz(prod);
   if ((uint64_t)e >= (uint64_t)P.num_edges) {  // rand >= 1, NaN, negative, or corrupt rowptr
     raise_flag(P.flags, WALK_B200_FLAG_BAD_EDGE);
+    if (P.num_edges <= 0) {  // nothing to clamp to (col may be NULL): park instead of gathering
+      parked = true;
+      return -1;
+    }
     e = e < 0 ? 0 : P.num_edges - 1;
   }
   const int64_t nxt = ld8(P.col + e, pol.stream);
@@ -290,6 +321,10 @@ __device__ __forceinline__ int64_t uniform_step_fused(const UniformParams& P, co
   int64_t e = rs + __float2ll_rz(prod);
   if ((uint64_t)e >= (uint64_t)P.num_edges) {
     raise_flag(P.flags, WALK_B200_FLAG_BAD_EDGE);
+    if (P.num_edges <= 0) {
+      parked = true;
+      return -1;
+    }
     e = e < 0 ? 0 : P.num_edges - 1;
   }
   const ulonglong2 rec = ld16(P.fused + e, pol.stream);
@@ -558,6 +593,7 @@ struct Node2vecParams {
   uint32_t max_attempts;
   int32_t batch_lanes, batch_trips;  // batching of the rare state paths (see the kernel)
   int32_t draw_loop;                 // REV: memory-free rejections consumed per trip
+  int32_t drain, drain_trips;        // pooled kernel: drain phase (bit 0 pack slots, bit 1 serve all), trips per round
   int64_t* n_out;
   int64_t* e_out;
   uint32_t* flags;
@@ -973,12 +1009,13 @@ template <bool FAST_DIV>
 __global__ void __launch_bounds__(kBlock) context_windows_kernel(const int64_t* __restrict__ walks,
                                                                  int64_t num_walks, int32_t row_len,
                                                                  int32_t cs, uint32_t magic, int32_t per_walk,
-                                                                 int64_t* __restrict__ windows) {
+                                                                 int64_t* __restrict__ windows, bool base_aligned) {
   const L2Policy pol = make_policies(2);  // the windows stream out once: evict-first
   for (int64_t w = blockIdx.y; w < num_walks; w += gridDim.y) {
     const int64_t* __restrict__ row = walks + w * row_len;
     int64_t* __restrict__ out = windows + w * (int64_t)per_walk;
-    const bool aligned = ((w * (int64_t)per_walk) & 1) == 0;  // 16-byte alignment of this walk's output
+    // 16-byte alignment of this walk's output (base_aligned: the matrix itself starts on a 16-byte boundary)
+    const bool aligned = base_aligned == (((w * (int64_t)per_walk) & 1) == 0);
     for (int32_t f = 2 * (blockIdx.x * kBlock + threadIdx.x); f < per_walk; f += 2 * gridDim.x * kBlock) {
       const int32_t j0 = FAST_DIV ? (int32_t)__umulhi((uint32_t)f, magic) : f / cs;
       const int32_t k0 = f - j0 * cs;

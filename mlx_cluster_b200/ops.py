@@ -35,6 +35,27 @@ def _stream_handle(stream, device) -> int:
     raise TypeError(f"stream must be None, a torch.cuda.Stream or a raw handle, not {type(stream).__name__}")
 
 
+def _sync_stream(stream, device) -> None:
+    """Wait for the stream the kernels were launched on (``None``: torch's current stream)."""
+    if stream is None:
+        torch.cuda.current_stream(device).synchronize()
+    elif isinstance(stream, torch.cuda.Stream):
+        stream.synchronize()
+    else:
+        torch.cuda.ExternalStream(int(stream), device=device).synchronize()
+
+
+def _take_flags(flags: torch.Tensor, stream, device) -> int:
+    """Read and clear a status word that kernels on ``stream`` may have written. The read waits for that
+    stream first: ``Tensor.item()`` alone only orders itself after torch's *current* stream."""
+    _sync_stream(stream, device)
+    f = int(flags.item())
+    if f:
+        flags.zero_()
+        torch.cuda.current_stream(device).synchronize()  # the clear lands before a later launch on another stream
+    return f
+
+
 def _require(t, name, dtype, device=None):
     if not isinstance(t, torch.Tensor):
         raise TypeError(f"{name} must be a torch.Tensor")
@@ -76,23 +97,26 @@ class WalkGraph:
         self.edgeset_buckets = 0
         self.colrev = None
         self.fused = None
+        self.rows_sorted = None   # None: not checked yet (see check_rows_sorted)
+        self.n2v_calls = 0        # node2vec calls served: edgeset="auto" builds the hash set on the second
         self._version = (rowptr._version, col._version)
         with torch.cuda.device(dev):
             self.flags = torch.zeros(1, dtype=torch.int32, device=dev)
+            torch.cuda.current_stream(dev).synchronize()  # the zero fill lands before a launch on another stream
             sh = _stream_handle(stream, dev)
             if validate:
                 self.validate(stream=stream)
+                self.rows_sorted = True
             if use_rowdesc and self.num_nodes > 0:
                 desc = torch.empty(self.num_nodes, dtype=torch.int64, device=dev)
                 _lib.check(_lib.lib().walk_b200_rowdesc_pack(
                     rowptr.data_ptr(), self.num_nodes, self.num_edges, desc.data_ptr(),
                     self.flags.data_ptr(), sh))
-                f = int(self.flags.item())
+                f = _take_flags(self.flags, stream, dev)
                 if f & _lib.FLAG_BAD_ROWPTR:
                     raise ValueError("rowptr is not a monotone prefix array ending at col.numel()")
                 if not (f & _lib.FLAG_DESC_OVERFLOW):
                     self.rowdesc = desc
-                self.flags.zero_()
             if edgeset and self.num_edges > 0:
                 self.build_edgeset(stream=stream)
             if fused and self.num_edges > 0:
@@ -108,8 +132,7 @@ class WalkGraph:
             csr = self.csr()
             _lib.check(_lib.lib().walk_b200_fused_build(C.byref(csr), rec.data_ptr(), self.flags.data_ptr(),
                                                         _stream_handle(stream, self.device)))
-            f = int(self.flags.item())
-            self.flags.zero_()
+            f = _take_flags(self.flags, stream, self.device)
             if f:
                 raise ValueError(f"fused record build failed, status flags 0x{f:x}: {describe_flags(f)}")
             self.fused = rec
@@ -125,8 +148,7 @@ class WalkGraph:
             csr = self.csr()
             _lib.check(_lib.lib().walk_b200_edgeset_build(C.byref(csr), table.data_ptr(), buckets,
                                                           self.flags.data_ptr(), _stream_handle(stream, self.device)))
-            f = int(self.flags.item())
-            self.flags.zero_()
+            f = _take_flags(self.flags, stream, self.device)
             if f:
                 raise ValueError(f"edge set build failed, status flags 0x{f:x}: {describe_flags(f)}")
             self.edgeset, self.edgeset_buckets = table, buckets
@@ -136,14 +158,14 @@ class WalkGraph:
                 rev = torch.empty(self.num_edges, dtype=torch.int32, device=self.device)
                 sh = _stream_handle(stream, self.device)
                 _lib.check(_lib.lib().walk_b200_revpos_build(C.byref(csr), rev.data_ptr(), self.flags.data_ptr(), sh))
-                f = int(self.flags.item())
-                self.flags.zero_()
+                f = _take_flags(self.flags, stream, self.device)
+                if self.rows_sorted is None:  # the build checks every row on its way
+                    self.rows_sorted = not (f & _lib.FLAG_UNSORTED_ROW)
                 if not f:
                     csr.revpos = rev.data_ptr()
                     joined = torch.empty(self.num_edges, dtype=torch.int64, device=self.device)
                     _lib.check(_lib.lib().walk_b200_colrev_build(C.byref(csr), joined.data_ptr(), self.flags.data_ptr(), sh))
-                    f = int(self.flags.item())
-                    self.flags.zero_()
+                    f = _take_flags(self.flags, stream, self.device)
                     if f:
                         raise ValueError(f"colrev build failed, status flags 0x{f:x}: {describe_flags(f)}")
                     self.colrev = joined
@@ -153,17 +175,41 @@ class WalkGraph:
                         _ptr(self.rowdesc), _lib.CSR_SYMMETRIC if self.symmetric else 0, 0,
                         _ptr(self.edgeset), self.edgeset_buckets, None, _ptr(self.fused), _ptr(self.colrev))
 
-    def validate(self, start: Optional[torch.Tensor] = None, *, check_sorted: bool = True, stream=None):
-        """Raise ValueError when the CSR (and, if given, the start nodes) is malformed."""
+    def _validate_flags(self, start, check_sorted, stream) -> int:
         with torch.cuda.device(self.device):
             flags = torch.zeros(1, dtype=torch.int32, device=self.device)
+            torch.cuda.current_stream(self.device).synchronize()  # the zero fill lands before a launch on another stream
             csr = self.csr()
             _lib.check(_lib.lib().walk_b200_csr_validate(
                 C.byref(csr), _ptr(start), 0 if start is None else start.numel(), int(check_sorted),
                 flags.data_ptr(), _stream_handle(stream, self.device)))
-            f = int(flags.item())
+            return _take_flags(flags, stream, self.device)
+
+    def validate(self, start: Optional[torch.Tensor] = None, *, check_sorted: bool = True, stream=None):
+        """Raise ValueError when the CSR (and, if given, the start nodes) is malformed."""
+        f = self._validate_flags(start, check_sorted, stream)
         if f:
             raise ValueError(f"malformed graph input, status flags 0x{f:x}: {describe_flags(f)}")
+
+    def check_rows_sorted(self, stream=None) -> bool:
+        """Whether every row of ``col`` is strictly ascending -- what the binary-search membership test of
+        node2vec needs, and what the reference's linear ``is_neighbor`` scan
+        (``random_walks/BiasedRandomWalk.cpp:20-28``) does not. Checked once per graph (one pass over the
+        CSR); any other defect found on the way (ids out of range, a broken ``rowptr``) raises."""
+        if self.rows_sorted is None:
+            f = self._validate_flags(None, True, stream)
+            other = f & ~_lib.FLAG_UNSORTED_ROW
+            if other:
+                raise ValueError(f"malformed graph input, status flags 0x{other:x}: {describe_flags(other)}")
+            self.rows_sorted = not (f & _lib.FLAG_UNSORTED_ROW)
+        return self.rows_sorted
+
+    def edgeset_fits(self) -> bool:
+        """Whether this device has room left for the edge hash set and the reverse positions (together
+        about 28 bytes per edge while they are built, 24 afterwards)."""
+        free, _ = torch.cuda.mem_get_info(self.device)
+        cached = torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+        return 28 * self.num_edges * 1.2 + (256 << 20) < free + cached
 
 
 def describe_flags(f: int) -> str:
@@ -253,8 +299,22 @@ def _as_cpu_tensor(a):
     return torch.from_numpy(np.ascontiguousarray(a))
 
 
+def _fingerprint(t: torch.Tensor) -> tuple:
+    """Cheap content sample of a host array (ends, and a position-weighted sum of at most 2^17 evenly spaced
+    entries): host arrays, numpy ones above all, carry no version counter, so an edit in place would
+    otherwise go unseen and a stale resident graph would be walked. A cached graph is a snapshot of the
+    arrays it was made from; an edit this sample misses needs ``clear_caches()`` or an explicit
+    :class:`HostGraph`."""
+    n = t.numel()
+    if n == 0:
+        return (0,)
+    sample = t[::max(1, n >> 16)]
+    weights = torch.arange(sample.numel(), dtype=torch.int64) % 1021 + 1
+    return (int(t[0]), int(t[-1]), int((sample * weights).sum()))
+
+
 def _host_graph(rowptr, col, symmetric, validate, edgeset=False, fused=False):
-    k = _key(rowptr, col, symmetric) + (bool(edgeset), bool(fused))
+    k = _key(rowptr, col, symmetric) + (bool(edgeset), bool(fused)) + _fingerprint(rowptr) + _fingerprint(col)
     g = _HOST_CACHE.get(k)
     if g is None:
         g = HostGraph(rowptr, col, symmetric=symmetric, edgeset=edgeset, fused=fused, validate=validate)
@@ -267,12 +327,10 @@ def _host_graph(rowptr, col, symmetric, validate, edgeset=False, fused=False):
     return g
 
 
-def read_status(graph: WalkGraph) -> int:
-    """Synchronise and return (then clear) the status flags kernels raised on this graph."""
-    f = int(graph.flags.item())
-    if f:
-        graph.flags.zero_()
-    return f
+def read_status(graph: WalkGraph, stream=None) -> int:
+    """Wait for ``stream`` (the one the walks were launched on; ``None`` = torch's current stream), then
+    return and clear the status flags kernels raised on this graph."""
+    return _take_flags(graph.flags, stream, graph.device)
 
 
 def _check_walk_length(walk_length):
@@ -283,17 +341,85 @@ def _check_walk_length(walk_length):
     return int(walk_length)
 
 
-def _finish(graph, out, e_out, check, return_edges):
+def _finish(graph, out, e_out, check, return_edges, stream=None):
     if check:
-        f = read_status(graph)
+        f = read_status(graph, stream)
         if f:
             raise RuntimeError(f"walk kernel raised status flags 0x{f:x}: {describe_flags(f)}")
     return (out, e_out) if return_edges else out
 
 
+def _devices(devices):
+    out = []
+    for d in devices:
+        d = torch.device("cuda", d) if isinstance(d, int) else torch.device(d)
+        if d.type != "cuda":
+            raise ValueError(f"devices must name CUDA devices, got {d}")
+        out.append(torch.device("cuda", torch.cuda.current_device() if d.index is None else d.index))
+    if not out:
+        raise ValueError("devices is empty")
+    return out
+
+
+_REPLICAS: "OrderedDict[tuple, tuple]" = OrderedDict()
+
+
+def _replica(rowptr, col, dev):
+    """The CSR on ``dev``: the caller's tensors if they live there, else a copy made once (device to
+    device, over NVLink where the GPUs are connected) and kept while the source tensors are unchanged."""
+    if rowptr.device == dev:
+        return rowptr, col
+    k = _key(rowptr, col, False) + (str(dev),)
+    hit = _REPLICAS.get(k)
+    if hit is None:
+        hit = (rowptr, col, rowptr.to(dev), col.to(dev))  # the source tensors are held so their addresses stay theirs
+        _REPLICAS[k] = hit
+        while len(_REPLICAS) > 2 * _CACHE_SIZE:
+            _REPLICAS.popitem(last=False)
+    else:
+        _REPLICAS.move_to_end(k)
+    return hit[2], hit[3]
+
+
+def _across_devices(call, rowptr, col, start, rand, L, devices, gather, return_edges, base, stride):
+    """One host thread drives several GPUs: device ``g`` of ``G`` walks the contiguous block
+    ``shard_range(n, G, g)`` of the start rows on a replica of the CSR (launches are asynchronous, so the
+    devices run at the same time); draws are indexed by the global row, so the blocks are exactly the rows
+    of the single-device result. ``gather=False`` returns the list of per-device blocks, ``gather=True``
+    one matrix on ``start``'s device (device-to-device copies, each ordered after its block's kernel)."""
+    from .sharding import shard_range
+    devs = _devices(devices)
+    n = start.numel()
+    home = start.device
+    blocks, edges = [], []
+    full = torch.empty((n, L + 1), dtype=torch.int64, device=home) if gather else None
+    full_e = torch.empty((n, L), dtype=torch.int64, device=home) if gather and return_edges else None
+    for r, dev in enumerate(devs):
+        b, e = shard_range(n, len(devs), r)
+        rp, cl = _replica(rowptr, col, dev)
+        s_blk = start[b:e].to(dev, non_blocking=True)
+        r_blk = None if rand is None else rand.reshape(n, -1)[b:e].to(dev, non_blocking=True)
+        # rank 0 of a gather on its own device writes its block in place
+        out = full[b:e] if gather and dev == home else None
+        res = call(rp, cl, s_blk, r_blk, base + b * stride, stride, out)
+        blocks.append(res[0] if return_edges else res)
+        if return_edges:
+            edges.append(res[1])
+    if not gather:
+        return list(zip(blocks, edges)) if return_edges else blocks
+    for r, dev in enumerate(devs):
+        b, e = shard_range(n, len(devs), r)
+        if blocks[r].data_ptr() != full[b:e].data_ptr():
+            full[b:e].copy_(blocks[r], non_blocking=True)
+        if return_edges:
+            full_e[b:e].copy_(edges[r], non_blocking=True)
+    return (full, full_e) if return_edges else full
+
+
 def random_walk(rowptr, col, start, rand, walk_length, *, stream=None, return_edges: bool = False,
                 check: bool = False, out: Optional[torch.Tensor] = None, graph: Optional[WalkGraph] = None,
-                fused: bool = False, seed: int = 0, walk_index_base: int = 0, walk_index_stride: int = 1):
+                fused: bool = False, seed: int = 0, walk_index_base: int = 0, walk_index_stride: int = 1,
+                validate: bool = False, devices=None, gather: bool = False):
     """Uniform CSR random walk (``random_walk`` of the reference, ``bindings.cpp:12-21``).
 
     Step ``l`` of walk ``w`` moves from ``v`` to ``col[rowptr[v] + int(rand[w, l] * deg(v))]``
@@ -309,11 +435,32 @@ def random_walk(rowptr, col, start, rand, walk_length, *, stream=None, return_ed
     (CUDA tensors only) lets the kernel generate the draws itself from a Philox stream keyed by
     ``seed`` and indexed by the global walk (``walk_index_base + row * walk_index_stride``);
     ``mlx_cluster_b200._lib.uniform_draws`` replays that stream on the host.
+    ``validate=True`` first checks the CSR and the start nodes on the device (the reference checks
+    nothing, ``random_walks/RandomWalk.cpp:33-38``) and raises ``ValueError`` on a malformed input.
+    ``devices=[...]`` (CUDA tensors only) splits the start rows in contiguous blocks over these GPUs of
+    this process, each walking a replica of the CSR, and returns the list of per-device blocks, or with
+    ``gather=True`` the one matrix on ``start``'s device; one process per GPU goes through
+    :func:`mlx_cluster_b200.sharded_walk` instead.
     """
     L = _check_walk_length(walk_length)
     if not isinstance(start, torch.Tensor) or not start.is_cuda:
-        return _random_walk_host(rowptr, col, start, rand, L, return_edges, out, fused)
+        if devices is not None:
+            raise ValueError("devices= needs CUDA tensors; host arrays walk on the resident graph's device")
+        return _random_walk_host(rowptr, col, start, rand, L, return_edges, out, fused, validate)
     dev = start.device
+    if devices is not None:
+        if graph is not None or out is not None:
+            raise ValueError("devices= builds its own per-device graphs and outputs: pass rowptr/col, not graph=/out=")
+        rp = _require(rowptr, "rowptr", torch.int64, dev)
+        cl = _require(col, "col", torch.int64, dev)
+        if rand is not None and rand.numel() != start.numel() * L:
+            raise ValueError(f"rand must hold n * walk_length = {start.numel() * L} values, has {rand.numel()}")
+
+        def call(rp_d, cl_d, s_blk, r_blk, b, st, o):
+            return random_walk(rp_d, cl_d, s_blk, r_blk, L, return_edges=return_edges, check=check, out=o, fused=fused,
+                               seed=seed, walk_index_base=b, walk_index_stride=st, validate=validate)
+        return _across_devices(call, rp, cl, start, rand, L, devices, gather, return_edges, int(walk_index_base),
+                               int(walk_index_stride))
     g = graph if graph is not None else prepare_graph(_require(rowptr, "rowptr", torch.int64, dev),
                                                       _require(col, "col", torch.int64, dev), fused=fused)
     _require(start, "start", torch.int64, g.device)
@@ -322,6 +469,8 @@ def random_walk(rowptr, col, start, rand, walk_length, *, stream=None, return_ed
         _require(rand, "rand", torch.float32, g.device)
         if rand.numel() != n * L:
             raise ValueError(f"rand must hold n * walk_length = {n * L} values, has {rand.numel()}")
+    if validate:
+        g.validate(start, check_sorted=False, stream=stream)
     with torch.cuda.device(dev):
         if out is None:
             out = torch.empty((n, L + 1), dtype=torch.int64, device=dev)
@@ -339,15 +488,42 @@ def random_walk(rowptr, col, start, rand, walk_length, *, stream=None, return_ed
             _lib.check(_lib.lib().walk_b200_uniform_walk(
                 C.byref(csr), _ptr(start), _ptr(rand), n, L, _ptr(out), _ptr(e_out),
                 g.flags.data_ptr(), _stream_handle(stream, dev)))
-    return _finish(g, out, e_out, check, return_edges)
+    return _finish(g, out, e_out, check, return_edges, stream)
+
+
+def _membership_ready(g: WalkGraph, edgeset, stream, allow_auto: bool = True) -> None:
+    """Bring a graph into a state the node2vec kernels answer exactly on.
+
+    ``edgeset=True`` builds the edge hash set now, ``False`` never does, ``"auto"`` (the default of
+    :func:`rejection_sampling`) builds it on the graph's second node2vec call when the device has room:
+    the set and the reverse positions that come with it triple the graph's memory and take about as long to
+    build as one fast walk launch, which pays from the second launch on (the first call of a graph that is
+    walked only once runs the binary-search kernel and allocates nothing). Without a hash set the membership
+    test is a binary search over ``col``, which needs every row sorted; the reference's linear scan does not
+    (``random_walks/BiasedRandomWalk.cpp:20-28``). So the rows are checked once per graph, and an unsorted
+    CSR gets the hash set (exact for any CSR) regardless -- or, with ``edgeset=False``, is refused."""
+    if g.edgeset is not None or g.num_edges == 0:
+        return
+    if edgeset is True:
+        g.build_edgeset(stream=stream)
+        return
+    if not g.check_rows_sorted(stream=stream):
+        if edgeset is False:
+            raise ValueError("a row of col is not sorted ascending: the binary-search membership test needs sorted "
+                             "rows; pass edgeset=True (or leave the default) to use the edge hash set instead")
+        g.build_edgeset(stream=stream)
+        return
+    if allow_auto and edgeset == "auto" and g.n2v_calls >= 1 and g.num_nodes < 2**32 - 1 and g.edgeset_fits():
+        g.build_edgeset(stream=stream)
 
 
 def rejection_sampling(rowptr, col, start, walk_length, p, q, *, stream=None, seed: int = 0,
                        walk_index_base: int = 0, walk_index_stride: int = 1, symmetric: bool = False,
-                       edgeset: bool = False,
+                       edgeset="auto",
                        return_edges: bool = False,
                        return_counters: bool = False, check: bool = False,
-                       out: Optional[torch.Tensor] = None, graph: Optional[WalkGraph] = None):
+                       out: Optional[torch.Tensor] = None, graph: Optional[WalkGraph] = None,
+                       validate: bool = False, devices=None, gather: bool = False):
     """node2vec biased walk by rejection sampling (``rejection_sampling`` of the reference,
     ``bindings.cpp:35-45``; loop at ``random_walks/BiasedRandomWalk.cpp:52-99``).
 
@@ -355,24 +531,50 @@ def rejection_sampling(rowptr, col, start, walk_length, p, q, *, stream=None, se
     Philox4x32-10 stream keyed by ``seed`` and indexed by (global walk index, step,
     attempt), so a call is reproducible, re-entrant and independent of how walks are
     sharded (row ``i`` of this call is global walk ``walk_index_base + i * walk_index_stride``).
-    Every row of
-    ``col`` must be sorted ascending. ``symmetric=True`` asserts an undirected graph and
-    lets the membership test search the previous node's row; ``edgeset=True`` builds (once
-    per graph, 16 bytes per edge) an exact edge hash set and tests membership with about
-    one 32-byte read instead, for any CSR; neither changes a result.
+    ``symmetric=True`` asserts an undirected graph and lets the membership test search the previous
+    node's row. ``edgeset`` chooses how "is the previous node a neighbour of the candidate" is answered:
+    ``True`` builds (once per graph, 16 bytes per edge, plus 8 for the reverse positions) an exact edge
+    hash set that answers with about one 32-byte read, for any CSR; ``False`` keeps the binary search
+    over ``col`` (rows must be sorted: checked once per graph, an unsorted CSR raises); ``"auto"``
+    (default) walks a graph's first call with the binary search and builds the hash set on its second
+    call if the device has room, and always builds it for a CSR whose rows are not sorted (a prepared
+    ``graph=`` is only checked for sorted rows and otherwise walked with the structures it has). None of
+    this changes a result. ``validate``, ``devices`` and ``gather`` as in :func:`random_walk`.
     Returns int64 ``[n, walk_length + 1]``.
     """
     L = _check_walk_length(walk_length)
     p, q = float(p), float(q)
+    if edgeset not in (True, False, "auto"):
+        raise ValueError("edgeset must be True, False or 'auto'")
     if not isinstance(start, torch.Tensor) or not start.is_cuda:
+        if devices is not None:
+            raise ValueError("devices= needs CUDA tensors; host arrays walk on the resident graph's device")
         return _rejection_sampling_host(rowptr, col, start, L, p, q, seed, walk_index_base, symmetric,
-                                        return_edges, out, edgeset, walk_index_stride)
+                                        return_edges, out, edgeset, walk_index_stride, validate)
     dev = start.device
+    if devices is not None:
+        if graph is not None or out is not None or return_counters:
+            raise ValueError("devices= builds its own per-device graphs and outputs: pass rowptr/col, "
+                             "not graph=/out=/return_counters=")
+        rp = _require(rowptr, "rowptr", torch.int64, dev)
+        cl = _require(col, "col", torch.int64, dev)
+
+        def call(rp_d, cl_d, s_blk, r_blk, b, st, o):
+            return rejection_sampling(rp_d, cl_d, s_blk, L, p, q, seed=seed, walk_index_base=b, walk_index_stride=st,
+                                      symmetric=symmetric, edgeset=edgeset, return_edges=return_edges, check=check,
+                                      out=o, validate=validate)
+        return _across_devices(call, rp, cl, start, None, L, devices, gather, return_edges, int(walk_index_base),
+                               int(walk_index_stride))
     g = graph if graph is not None else prepare_graph(_require(rowptr, "rowptr", torch.int64, dev),
                                                       _require(col, "col", torch.int64, dev),
-                                                      symmetric=symmetric, edgeset=edgeset)
+                                                      symmetric=symmetric)
     _require(start, "start", torch.int64, g.device)
     n = start.numel()
+    if validate:
+        g.validate(start, check_sorted=False, stream=stream)
+    # a graph the caller prepared keeps the structures it was given, except that unsorted rows get the hash set
+    _membership_ready(g, edgeset, stream, allow_auto=graph is None)
+    g.n2v_calls += 1
     with torch.cuda.device(dev):
         if out is None:
             out = torch.empty((n, L + 1), dtype=torch.int64, device=dev)
@@ -382,12 +584,15 @@ def rejection_sampling(rowptr, col, start, walk_length, p, q, *, stream=None, se
                 raise ValueError("out has the wrong size")
         e_out = torch.empty((n, L), dtype=torch.int64, device=dev) if return_edges else None
         counters = torch.zeros(len(_lib.COUNTER_NAMES), dtype=torch.int64, device=dev) if return_counters else None
+        if counters is not None:
+            torch.cuda.current_stream(dev).synchronize()  # zeroed before a launch on another stream adds to them
         csr = g.csr()
         _lib.check(_lib.lib().walk_b200_node2vec_walk(
             C.byref(csr), _ptr(start), n, L, p, q, int(seed) & (2**64 - 1), int(walk_index_base),
             int(walk_index_stride), _ptr(out), _ptr(e_out), g.flags.data_ptr(), _ptr(counters), _stream_handle(stream, dev)))
-    res = _finish(g, out, e_out, check, return_edges)
+    res = _finish(g, out, e_out, check, return_edges, stream)
     if return_counters:
+        _sync_stream(stream, dev)
         cnt = dict(zip(_lib.COUNTER_NAMES, (int(x) for x in counters.tolist())))
         return (*res, cnt) if isinstance(res, tuple) else (res, cnt)
     return res
@@ -404,14 +609,14 @@ def _host_out(n, L, out):
     return out
 
 
-def _random_walk_host(rowptr, col, start, rand, L, return_edges, out, fused=False):
+def _random_walk_host(rowptr, col, start, rand, L, return_edges, out, fused=False, validate=False):
     rowptr, col = _as_cpu_tensor(rowptr), _as_cpu_tensor(col)
     start = _require(_as_cpu_tensor(start), "start", torch.int64)
     rand = _require(_as_cpu_tensor(rand), "rand", torch.float32)
     n = start.numel()
     if rand.numel() != n * L:
         raise ValueError(f"rand must hold n * walk_length = {n * L} values, has {rand.numel()}")
-    g = _host_graph(rowptr, col, False, False, fused=fused)
+    g = _host_graph(rowptr, col, False, 2 if validate else 0, fused=fused)
     out = _host_out(n, L, out)
     e_out = torch.empty((n, L), dtype=torch.int64, pin_memory=True) if return_edges else None
     with torch.cuda.device(g.device):
@@ -420,11 +625,18 @@ def _random_walk_host(rowptr, col, start, rand, L, return_edges, out, fused=Fals
 
 
 def _rejection_sampling_host(rowptr, col, start, L, p, q, seed, base, symmetric, return_edges, out, edgeset=False,
-                             stride=1):
+                             stride=1, validate=False):
     rowptr, col = _as_cpu_tensor(rowptr), _as_cpu_tensor(col)
     start = _require(_as_cpu_tensor(start), "start", torch.int64)
     n = start.numel()
-    g = _host_graph(rowptr, col, symmetric, False, edgeset)
+    if edgeset == "auto":
+        # a resident graph is made to be walked again and again: build the hash set with the upload when the
+        # graph (with it, about 5x the bytes of col) fits half the device, else keep the binary search
+        free, _ = torch.cuda.mem_get_info()
+        edgeset = col.numel() * 40 + rowptr.numel() * 16 < free // 2
+    # without the hash set the membership test is a binary search: the upload then checks that rows are sorted
+    # (validate mode 1) and refuses the graph otherwise; with it, rows may come in any order (mode 2)
+    g = _host_graph(rowptr, col, symmetric, 1 if not edgeset else (2 if validate else 0), bool(edgeset))
     out = _host_out(n, L, out)
     e_out = torch.empty((n, L), dtype=torch.int64, pin_memory=True) if return_edges else None
     with torch.cuda.device(g.device):

@@ -49,74 +49,95 @@ def shard_rows(num_walks: int, world_size: int, rank: int, layout: str = "block"
 
 def gather_rows_cyclic(shard: torch.Tensor, num_rows: int, *, group=None, dst: int = 0,
                        chunk_rows: int = 1 << 22):
-    """Collect cyclic shards on ``dst``: rank r's rows land at ``r::world``. Shards arrive in
-    a contiguous staging buffer of one shard and are interleaved by a strided copy."""
+    """Collect cyclic shards on ``dst``: rank r's rows land at ``r::world``. A received message is a
+    contiguous run of one rank's rows, so the cyclic layout cannot be received in place: all shards
+    arrive, in one batch of point-to-point messages, in a staging buffer and are interleaved by one
+    strided copy per source. Costs a second copy of the matrix on ``dst``; the block layout
+    (:func:`gather_rows`) needs neither the staging nor the interleave."""
     world, rank = _world(group)
     if world == 1:
         return shard
     width = shard.shape[1]
+    peer = (lambda r: dist.get_global_rank(group, r)) if group else (lambda r: r)
     if rank != dst:
-        ops = [dist.P2POp(dist.isend, shard[c0:min(shard.shape[0], c0 + chunk_rows)],
-                          dist.get_global_rank(group, dst) if group else dst, group)
+        ops = [dist.P2POp(dist.isend, shard[c0:min(shard.shape[0], c0 + chunk_rows)], peer(dst), group)
                for c0 in range(0, shard.shape[0], chunk_rows)]
         for req in (dist.batch_isend_irecv(ops) if ops else []):
             req.wait()
         return None
-    full = torch.empty((num_rows, width), dtype=shard.dtype, device=shard.device)
-    full[rank::world].copy_(shard)
+    counts = [_lib.shard_count_cyclic(num_rows, world, r) for r in range(world)]
+    stage = torch.empty((sum(c for r, c in enumerate(counts) if r != dst), width), dtype=shard.dtype,
+                        device=shard.device)
+    ops, at, where = [], 0, {}
     for r in range(world):
-        if r == dst:
+        if r == dst or counts[r] == 0:
             continue
-        count = _lib.shard_count_cyclic(num_rows, world, r)
-        if count == 0:
-            continue
-        stage = torch.empty((count, width), dtype=shard.dtype, device=shard.device)
-        ops = [dist.P2POp(dist.irecv, stage[c0:min(count, c0 + chunk_rows)],
-                          dist.get_global_rank(group, r) if group else r, group)
-               for c0 in range(0, count, chunk_rows)]
-        for req in dist.batch_isend_irecv(ops):
-            req.wait()
-        full[r::world].copy_(stage)
+        where[r] = at
+        for c0 in range(0, counts[r], chunk_rows):
+            c1 = min(counts[r], c0 + chunk_rows)
+            ops.append(dist.P2POp(dist.irecv, stage[at + c0:at + c1], peer(r), group))
+        at += counts[r]
+    reqs = dist.batch_isend_irecv(ops) if ops else []
+    full = torch.empty((num_rows, width), dtype=shard.dtype, device=shard.device)
+    full[rank::world].copy_(shard)  # overlaps the transfers
+    for req in reqs:
+        req.wait()
+    for r, at in where.items():
+        full[r::world].copy_(stage[at:at + counts[r]])
     return full
 
 
 def gather_rows(shard: torch.Tensor, num_rows: int, *, group=None, dst: int = 0,
-                out: Optional[torch.Tensor] = None, chunk_rows: int = 1 << 22):
+                out: Optional[torch.Tensor] = None, chunk_rows: int = 1 << 22, row_range=None):
     """Collect row shards (``shard_range`` layout) on rank ``dst``.
 
     Returns the ``[num_rows, width]`` matrix on ``dst`` and ``None`` elsewhere. When
-    ``out`` is given on ``dst`` and ``shard`` already is the matching slice of ``out``,
-    no local copy is made. Messages are cut into pieces of ``chunk_rows`` rows.
+    ``out`` is given on ``dst`` and ``shard`` already is the matching slice of ``out`` (the
+    destination's own walk kernel wrote it there), no local copy is made. Every other rank's rows are
+    received straight at their row offset; all messages (pieces of ``chunk_rows`` rows) are posted as one
+    batch, so the transfers of all sources run at the same time and the destination's inbound link is
+    the bound. ``row_range=(lo, hi)`` gathers only the global rows ``[lo, hi)`` into a
+    ``[hi - lo, width]`` matrix: a walk matrix larger than one GPU's memory cannot be gathered whole.
     """
     world, rank = _world(group)
     width = shard.shape[1]
+    lo, hi = (0, num_rows) if row_range is None else (int(row_range[0]), int(row_range[1]))
+    if not 0 <= lo <= hi <= num_rows:
+        raise ValueError(f"row_range {row_range} outside [0, {num_rows}]")
     if world == 1:
+        part = shard[lo:hi]
         if out is None:
-            return shard
-        if out.data_ptr() != shard.data_ptr():
-            out.copy_(shard)
+            return part
+        if out.data_ptr() != part.data_ptr():
+            out.copy_(part)
         return out
+    peer = (lambda r: dist.get_global_rank(group, r)) if group else (lambda r: r)
     ops = []
     if rank == dst:
         if out is None:
-            out = torch.empty((num_rows, width), dtype=shard.dtype, device=shard.device)
-        b, e = shard_range(num_rows, world, rank)
-        mine = out[b:e]
-        if mine.data_ptr() != shard.data_ptr():
-            mine.copy_(shard)
+            out = torch.empty((hi - lo, width), dtype=shard.dtype, device=shard.device)
+        elif out.shape[0] != hi - lo:
+            raise ValueError(f"out has {out.shape[0]} rows, the gathered range has {hi - lo}")
         for r in range(world):
-            if r == dst:
-                continue
             rb, re = shard_range(num_rows, world, r)
-            for c0 in range(rb, re, chunk_rows):
-                c1 = min(re, c0 + chunk_rows)
-                ops.append(dist.P2POp(dist.irecv, out[c0:c1], dist.get_global_rank(group, r) if group else r, group))
+            b, e = max(rb, lo), min(re, hi)  # this rank's part of the range
+            if b >= e:
+                continue
+            if r == dst:
+                mine = shard[b - rb:e - rb]
+                if out[b - lo:e - lo].data_ptr() != mine.data_ptr():
+                    out[b - lo:e - lo].copy_(mine)
+                continue
+            for c0 in range(b, e, chunk_rows):
+                c1 = min(e, c0 + chunk_rows)
+                ops.append(dist.P2POp(dist.irecv, out[c0 - lo:c1 - lo], peer(r), group))
     else:
-        b, e = shard_range(num_rows, world, rank)
-        assert shard.shape[0] == e - b, "shard does not match shard_range"
-        for c0 in range(0, e - b, chunk_rows):
-            c1 = min(e - b, c0 + chunk_rows)
-            ops.append(dist.P2POp(dist.isend, shard[c0:c1], dist.get_global_rank(group, dst) if group else dst, group))
+        rb, re = shard_range(num_rows, world, rank)
+        assert shard.shape[0] == re - rb, "shard does not match shard_range"
+        b, e = max(rb, lo), min(re, hi)
+        for c0 in range(b, e, chunk_rows):
+            c1 = min(e, c0 + chunk_rows)
+            ops.append(dist.P2POp(dist.isend, shard[c0 - rb:c1 - rb], peer(dst), group))
     if ops:
         for req in dist.batch_isend_irecv(ops):
             req.wait()

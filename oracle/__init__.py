@@ -26,7 +26,7 @@ _ref = None
 
 COUNTER_NAMES = (
     "attempts", "membership_ref", "membership_needed", "scan_elems", "bsearch_probes",
-    "steps_deg0", "steps_deg1", "steps_sampled", "steps_first",
+    "steps_deg0", "steps_deg1", "steps_sampled", "steps_first", "steps_capped",
 )
 
 
@@ -50,7 +50,7 @@ def _load_oracle():
         lib.oracle_counter_count.restype = C.c_int
         lib.oracle_node2vec_walk.argtypes = [_I64P, _I64P, _I64P, C.c_int64, C.c_int, C.c_double,
                                              C.c_double, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64,
-                                             _I64P, C.c_void_p, C.c_void_p]
+                                             _I64P, C.c_void_p, C.c_void_p, C.c_uint32]
         assert lib.oracle_counter_count() == len(COUNTER_NAMES)
         _oracle = lib
     return _oracle
@@ -127,9 +127,11 @@ def uniform_walk(rowptr, col, start, rand, walk_length: int, return_edges: bool 
 def node2vec_walk(rowptr, col, start, walk_length: int, p: float, q: float, *, seed: int = 0,
                   walk_index_base: int = 0, walk_index_stride: int = 1, draw_mode: int = 1,
                   return_edges: bool = False,
-                  return_counters: bool = False):
+                  return_counters: bool = False, max_attempts: int = 0):
     """draw_mode 1: Philox stream (key=seed, counter=(walk, step, attempt));
-    draw_mode 0: libc rand() in the reference's call order (seed it with ``srand``)."""
+    draw_mode 0: libc rand() in the reference's call order (seed it with ``srand``).
+    ``max_attempts`` 0 is the reference's unbounded rejection loop; a positive value makes a step
+    stand still (edge id -1) once that many candidates were rejected, as the CUDA path does."""
     lib = _load_oracle()
     rowptr, col, start = _i64(rowptr), _i64(col), _i64(start)
     n = start.shape[0]
@@ -140,7 +142,8 @@ def node2vec_walk(rowptr, col, start, walk_length: int, p: float, q: float, *, s
         col = np.zeros(1, dtype=np.int64)
     lib.oracle_node2vec_walk(rowptr, col, start if n else np.zeros(1, np.int64), n, walk_length,
                              p, q, draw_mode, seed, walk_index_base, walk_index_stride,
-                             n_out if n_out.size else np.zeros(1, np.int64), _opt(e_out), cnt.ctypes.data)
+                             n_out if n_out.size else np.zeros(1, np.int64), _opt(e_out), cnt.ctypes.data,
+                             int(max_attempts))
     res = [n_out]
     if return_edges:
         res.append(e_out)

@@ -138,6 +138,7 @@ enum {
   CNT_STEPS_DEG1,
   CNT_STEPS_SAMPLED,     /* steps l >= 1 with deg >= 2 */
   CNT_STEPS_FIRST,       /* step 0 with deg >= 1 */
+  CNT_STEPS_CAPPED,      /* steps given up after max_attempts rejections (never with max_attempts = 0) */
   CNT_COUNT
 };
 
@@ -147,12 +148,15 @@ int oracle_counter_count(void) { return CNT_COUNT; }
  * draw_mode 0: libc rand() in the reference's call order (caller seeds with srand()).
  * draw_mode 1: Philox stream above with global walk index walk_index_base + row * walk_index_stride.
  * counters: CNT_COUNT int64 slots, may be NULL.
+ * max_attempts: 0 = the reference's unbounded while(true) (random_walks/BiasedRandomWalk.cpp:80). A positive
+ * value restates the one deviation of the CUDA path: a step whose first max_attempts candidates are all
+ * rejected stands still (x = v, edge id -1), where the reference would keep drawing.
  */
 void oracle_node2vec_walk(const int64_t* rowptr, const int64_t* col, const int64_t* start,
                           int64_t n, int walk_length, double p, double q,
                           int draw_mode, uint64_t seed, uint64_t walk_index_base,
                           uint64_t walk_index_stride, int64_t* n_out, int64_t* e_out /* may be NULL */,
-                          int64_t* counters /* may be NULL */) {
+                          int64_t* counters /* may be NULL */, uint32_t max_attempts) {
   const int64_t L = walk_length;
   double prob[3];
   oracle_node2vec_thresholds(p, q, prob);
@@ -211,6 +215,12 @@ void oracle_node2vec_walk(const int64_t* rowptr, const int64_t* col, const int64
           cnt[CNT_MEMBERSHIP_REF]++;
           if (linear_is_neighbor(rowptr, col, x, t, &cnt[CNT_SCAN_ELEMS]) && r < prob_1) break;
           if (r < prob_2) break;
+          if (max_attempts && a + 1 >= max_attempts) { /* not in the reference: give up, stand still */
+            x = v;
+            e = -1;
+            cnt[CNT_STEPS_CAPPED]++;
+            break;
+          }
         }
       }
       n_out[w * (L + 1) + l + 1] = x;

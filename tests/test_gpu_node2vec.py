@@ -24,6 +24,9 @@ def _reset_tuning():
     _lib.set_tuning("n2v_rev", 1)
     _lib.set_tuning("n2v_pool", 1)
     _lib.set_tuning("l2_hints", 3)
+    _lib.set_tuning("n2v_drain", 3)
+    _lib.set_tuning("n2v_drain_trips", 8)
+    _lib.set_tuning("n2v_max_attempts", 1 << 22)
 
 
 def run_gpu(dev, rowptr, col, start, L, p, q, *, seed=0, base=0, symmetric=False, rowdesc=True,
@@ -87,6 +90,43 @@ def test_reference_api_signature(cuda, golden):
     for p, q in [(0.0, 1.0), (1.0, float("nan")), (-1.0, 1.0)]:
         with pytest.raises(_lib.WalkError):
             rejection_sampling(t(g["rowptr2"]), t(g["col2"]), t(g["start2"]), 5, p, q)
+
+
+@pytest.mark.parametrize("cap", [1, 2, 4])
+@pytest.mark.parametrize("member", list(MEMBERSHIP))
+def test_attempt_cap_stands_still_and_raises_the_flag(cuda, golden, member, cap):
+    """The reference's rejection loop is unbounded (BiasedRandomWalk.cpp:80); the CUDA path gives a step up
+    after a fixed number of rejections. With the cap lowered to a handful the limit runs out on many steps:
+    those stand still with edge id -1, the flag is raised, and everything else is the restatement's walk
+    under the same cap."""
+    g = golden
+    from mlx_cluster_b200 import read_status
+    _lib.set_tuning("n2v_max_attempts", cap)
+    n_o, e_o, cnt = oracle.node2vec_walk(g["rowptr2"], g["col2"], g["start2"], 20, 0.25, 4.0, seed=11,
+                                         return_edges=True, return_counters=True, max_attempts=cap)
+    assert cnt["steps_capped"] > 100
+    kw = dict(MEMBERSHIP[member])
+    _lib.set_tuning("n2v_rev", 2 if kw.pop("rev", True) else 0)
+    _lib.set_tuning("n2v_pool", 2 if kw.pop("pool", False) else 0)
+    graph = WalkGraph(torch.from_numpy(g["rowptr2"]).to(cuda), torch.from_numpy(g["col2"]).to(cuda), **kw)
+    st = torch.from_numpy(g["start2"]).to(cuda)
+    for edges in (True, False):
+        res = rejection_sampling(None, None, st, 20, 0.25, 4.0, graph=graph, seed=11, return_edges=edges)
+        flags = read_status(graph)
+        assert flags == _lib.FLAG_ATTEMPT_CAP
+        n = (res[0] if edges else res).cpu().numpy()
+        np.testing.assert_array_equal(n, n_o)
+        if edges:
+            e = res[1].cpu().numpy()
+            np.testing.assert_array_equal(e, e_o)
+            capped = (e == -1) & (np.diff(g["rowptr2"])[n[:, :-1]] > 0)
+            assert capped.sum() == cnt["steps_capped"]
+            assert (n[:, 1:][capped] == n[:, :-1][capped]).all()
+    with pytest.raises(RuntimeError, match="attempt cap"):
+        rejection_sampling(None, None, st, 20, 0.25, 4.0, graph=graph, seed=11, check=True)
+    # with the default cap nothing is given up and no flag is raised
+    _lib.set_tuning("n2v_max_attempts", 1 << 22)
+    rejection_sampling(None, None, st, 20, 0.25, 4.0, graph=graph, seed=11, check=True)
 
 
 def test_shard_invariance_and_seed(cuda, golden):
@@ -270,6 +310,19 @@ def test_properties_at_scale(cuda):
     _lib.set_tuning("n2v_idx", 1)
     assert torch.equal(out, rejection_sampling(rowptr, col, start, L, 0.25, 4.0, seed=3, symmetric=True))
     assert torch.equal(out, rejection_sampling(None, None, start, L, 0.25, 4.0, graph=hashed, seed=3))
+    # every 997th row of the pooled kernel's matrix (with and without its drain phase) and of the per-lane
+    # kernel's against the CPU restatement, which is handed the same global walk indices 0, 997, ...
+    rp_h, cl_h = rowptr.cpu().numpy(), col.cpu().numpy()
+    picked = torch.arange(0, n_nodes, 997, device=cuda)
+    want = oracle.node2vec_walk(rp_h, cl_h, picked.cpu().numpy(), L, 0.25, 4.0, seed=3, walk_index_stride=997)
+    _lib.set_tuning("n2v_idx", 0)
+    for pool, drain, trips in ((2, 3, 8), (2, 0, 8), (2, 1, 1), (2, 2, 3), (2, 3, 64), (0, 0, 8)):
+        _lib.set_tuning("n2v_pool", pool)
+        _lib.set_tuning("n2v_drain", drain)
+        _lib.set_tuning("n2v_drain_trips", trips)
+        got = rejection_sampling(None, None, start, L, 0.25, 4.0, graph=hashed, seed=3, check=True)
+        assert torch.equal(got, out), (pool, drain, trips)
+        np.testing.assert_array_equal(got[picked].cpu().numpy(), want)
     # a sub-sample of rows against the CPU restatement
     rows = torch.arange(0, n_nodes, 997, device=cuda)
     n_o = oracle.node2vec_walk(rowptr.cpu().numpy(), col.cpu().numpy(), rows.cpu().numpy(), L, 0.25, 4.0, seed=3,

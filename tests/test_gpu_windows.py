@@ -23,6 +23,26 @@ def test_windows_match_numpy_sliding_window(cuda, n, L, cs):
     assert _lib.launch_count() == before + (1 if n else 0)
 
 
+@pytest.mark.parametrize("n,L,cs", [(33, 20, 10), (257, 41, 7), (64, 9, 2), (5, 12, 13)])
+def test_windows_into_a_view_that_starts_at_an_odd_element(cuda, n, L, cs):
+    """``out`` may be a view that begins 8 bytes into a larger buffer: the pairs the kernel writes with one
+    16-byte store are then the other ones, and nothing else of the buffer is touched."""
+    rng = np.random.default_rng(n + L + cs)
+    walks = rng.integers(0, 1 << 40, (n, L + 1)).astype(np.int64)
+    want = np.lib.stride_tricks.sliding_window_view(walks, cs, axis=1).reshape(-1, cs)
+    buf = torch.full((want.size + 2,), -9, dtype=torch.int64, device=cuda)
+    assert buf.data_ptr() % 16 == 0
+    view = buf[1:-1]
+    got = context_windows(torch.from_numpy(walks).to(cuda), cs, out=view)
+    np.testing.assert_array_equal(got.cpu().numpy().reshape(-1, cs), want)
+    assert int(buf[0]) == -9 and int(buf[-1]) == -9
+    # and the walks themselves may be such a view
+    wbuf = torch.zeros(walks.size + 1, dtype=torch.int64, device=cuda)
+    wbuf[1:] = torch.from_numpy(walks.reshape(-1)).to(cuda)
+    got2 = context_windows(wbuf[1:].view(n, L + 1), cs)
+    np.testing.assert_array_equal(got2.cpu().numpy(), want)
+
+
 def test_windows_argument_errors(cuda):
     walks = torch.zeros((4, 6), dtype=torch.int64, device=cuda)
     with pytest.raises(ValueError):

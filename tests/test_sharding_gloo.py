@@ -74,6 +74,13 @@ def _worker(rank, world, port, n_rows, L, q):
                                        start_is_sharded=True, num_walks=n_rows, gather=True, dst=world - 1)
         if rank == world - 1:
             ok = ok and np.array_equal(got.numpy(), oracle.uniform_walk(rowptr, col, start.numpy(), rand.numpy(), L))
+        # a caller-chosen row range (what a matrix too large for one device is gathered by), chunked messages
+        for lo, hi in ((0, n_rows), (n_rows // 3, n_rows - n_rows // 4), sharding.shard_range(n_rows, world, 1), (0, 0)):
+            part = sharding.gather_rows(shard, n_rows, row_range=(lo, hi), chunk_rows=5)
+            if rank == 0:
+                ok = ok and part is not None and np.array_equal(part.numpy(), full_expected[lo:hi])
+            else:
+                ok = ok and part is None
         q.put((rank, bool(ok)))
     finally:
         dist.destroy_process_group()
