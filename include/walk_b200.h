@@ -261,10 +261,13 @@ int walk_b200_csr_build(const int64_t* src, const int64_t* dst, int64_t num_inpu
  * only its own batch: start (+ rand) host->device and the walk matrix device->host,
  * in slabs so that copies overlap the kernel. start and rand should be pinned
  * (cudaHostAlloc / cudaHostRegister) for the uploads to overlap.
- * When every id fits 31 bits the matrices cross the bus as int32 into pinned staging
- * owned by the graph and host threads of the library widen them into the caller's
- * int64 buffers (which may then be pageable); node2vec runs as one launch whose
- * finished slabs are copied out while it goes on, and keeps the int32 matrices in
+ * When every id fits 31 bits the matrices can cross the bus as int32 into pinned staging
+ * owned by the graph, host threads of the library widening them into the caller's
+ * int64 buffers (which may then be pageable): half the bytes on the bus, twice the
+ * traffic in host memory. Which of the two transports is faster depends on the machine
+ * and on how many processes share its host memory, so by default (host_narrow = 2) a
+ * short measurement at graph creation decides. node2vec runs as one launch whose
+ * finished slabs are copied out while it goes on, and keeps the matrices in
  * device memory for the duration of the call. Results are identical either way. A
  * call returns when the caller's buffers are written; on a non-zero return their
  * contents are unspecified.
@@ -281,6 +284,15 @@ int walk_b200_graph_destroy(walk_b200_graph* g);
 /* Device view of a resident graph (pointers owned by the graph). */
 int walk_b200_graph_csr(const walk_b200_graph* g, walk_b200_csr* out);
 int walk_b200_graph_device_bytes(const walk_b200_graph* g, int64_t* bytes);
+
+/* Transport the host entry points use for this graph's walk matrices (1 = int32 on the bus plus widening threads,
+ * 0 = int64 straight into the caller's buffers) under the current host_narrow tuning, and the two rates measured
+ * when the graph was created (GB/s; 0 if host_narrow was not 2 then): pinned device-to-host copy, and int64
+ * output of the widening threads. Any result pointer may be NULL. */
+int walk_b200_graph_host_transport(const walk_b200_graph* g, int32_t* narrow, double* d2h_gbs, double* widen_gbs);
+/* Output rate (GB/s of int64 written) of the widening threads on `out_bytes` of int64, with the current
+ * host_threads tuning: the host-side ceiling of the int32 transport on this machine right now. */
+int walk_b200_host_widen_probe(size_t out_bytes, double* out_gbs);
 
 int walk_b200_uniform_walk_host(walk_b200_graph* g, const int64_t* h_start, const float* h_rand,
                                 int64_t num_walks, int32_t walk_length, int64_t* h_n_out,
@@ -382,11 +394,9 @@ int walk_b200_gather_probe_ex(size_t array_bytes, int32_t iters, int32_t chains,
  *   uniform_variant, uniform_fused, l2_hints, l2_fetch_granularity, use_rowdesc
  *   n2v_idx, n2v_member, n2v_rev, n2v_pool (0 per-lane kernel, 1 pooled kernel where it wins, 2 always),
  *   n2v_batch_lanes, n2v_batch_trips, n2v_draw_loop, n2v_blocks_per_sm,
- *   n2v_drain (pooled kernel once the walk queue is dry: bit 0 packs a block's remaining walks into few warps,
- *   bit 1 lets a warp with at most 32 of them advance every one each trip; 0 = neither), n2v_drain_trips,
  *   n2v_max_attempts (rejections after which a step gives up, at most WALK_B200_MAX_ATTEMPTS: the one key that
  *   can change a result, and only for steps that reach the cap, which raise WALK_B200_FLAG_ATTEMPT_CAP)
- *   host_slab_mb, host_narrow (int32 on the bus), host_threads (widening threads, 0 = min(16, cores)),
+ *   host_slab_mb, host_narrow (1 int32 on the bus, 0 int64, 2 measured at graph creation), host_threads (widening threads, 0 = min(16, cores)),
  *   host_single_launch (node2vec host entry as one launch), host_resident_mb (its device-memory limit) */
 int walk_b200_set_tuning(const char* key, int32_t value);
 int walk_b200_get_tuning(const char* key, int32_t* value);

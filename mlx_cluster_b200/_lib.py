@@ -28,6 +28,7 @@ EXPORTS = (
     "walk_b200_node2vec_thresholds", "walk_b200_shard_range", "walk_b200_shard_count_cyclic",
     "walk_b200_graph_create", "walk_b200_graph_destroy", "walk_b200_graph_csr",
     "walk_b200_graph_device_bytes", "walk_b200_uniform_walk_host", "walk_b200_node2vec_walk_host",
+    "walk_b200_graph_host_transport", "walk_b200_host_widen_probe",
     "walk_b200_l2_window_set", "walk_b200_l2_window_clear",
     "walk_b200_set_tuning", "walk_b200_get_tuning",
     "walk_b200_uniform_walk_noalloc", "walk_b200_gather_probe", "walk_b200_gather_probe_ex", "walk_b200_context_windows",
@@ -95,6 +96,8 @@ def lib():
     L.walk_b200_graph_device_bytes.argtypes = [vp, C.POINTER(i64)]
     L.walk_b200_uniform_walk_host.argtypes = [vp, vp, vp, i64, i32, vp, vp]
     L.walk_b200_node2vec_walk_host.argtypes = [vp, vp, i64, i32, dbl, dbl, u64, u64, u64, vp, vp]
+    L.walk_b200_graph_host_transport.argtypes = [vp, C.POINTER(i32), C.POINTER(dbl), C.POINTER(dbl)]
+    L.walk_b200_host_widen_probe.argtypes = [C.c_size_t, C.POINTER(dbl)]
     L.walk_b200_l2_window_set.argtypes = [vp, C.c_size_t, C.c_float, vp, C.POINTER(C.c_size_t)]
     L.walk_b200_l2_window_clear.argtypes = [vp]
     L.walk_b200_uniform_walk_noalloc.argtypes = [vp, vp, i64, i64, vp, vp, i64, i32, vp, vp, vp, vp]
@@ -174,6 +177,26 @@ def gather_probe(array_bytes: int = 2 << 30, iters: int = 32, *, chains: int = 1
     r = C.c_double(0.0)
     check(lib().walk_b200_gather_probe_ex(array_bytes, iters, chains, gather_bytes, fetch_bytes, threads_per_sm,
                                           C.byref(r)))
+    return float(r.value)
+
+
+def host_transport(graph_handle) -> int:
+    """1 if the host entry points move this graph's walk matrices as int32 (widened on the host), 0 if as int64."""
+    n = C.c_int32(0)
+    check(lib().walk_b200_graph_host_transport(graph_handle, C.byref(n), None, None))
+    return int(n.value)
+
+
+def host_transport_rates(graph_handle):
+    """(pinned device-to-host GB/s, widening threads' int64 output GB/s) measured when the graph was created."""
+    d, w = C.c_double(0.0), C.c_double(0.0)
+    check(lib().walk_b200_graph_host_transport(graph_handle, None, C.byref(d), C.byref(w)))
+    return float(d.value), float(w.value)
+
+
+def host_widen_probe(out_bytes: int = 256 << 20) -> float:
+    r = C.c_double(0.0)
+    check(lib().walk_b200_host_widen_probe(out_bytes, C.byref(r)))
     return float(r.value)
 
 

@@ -6,20 +6,12 @@
 // its 32 fixed lanes are on and about 12 lanes do useful work per instruction; here a trip executes one
 // path with most lanes busy. Same Philox draws, same decisions, same outputs.
 //
-// Drain phase (P.drain, on by default). When the launch-wide queue is dry every warp still holds walks at a
-// random point of their steps, and the pool of each warp empties slowly: a warp with three live slots
-// issues the same instructions per trip as one with sixty, so the machine stays issue-bound while doing
-// less and less. Once a warp learns that the queue is dry (from its own refill or from a flag another
-// warp of its block set) it leaves the free-running loop; from then on the warps of a block proceed in
-// rounds of P.drain_trips trips separated by block barriers, and at each boundary the live slots of the
-// block are packed into as few warps as hold them (slot state is plain shared memory, so a move is a
-// copy of PF_COUNT words). Warps left without slots wait at the next barrier and issue nothing; a warp
-// with at most 32 live slots serves every one of them each trip whatever its class. Every warp of a
-// block executes the same sequence of barriers (all decisions between barriers are taken from shared
-// counts read after a barrier), and no warp waits for anything but those barriers.
+// The kernel runs at the register limit of six blocks per SM (40) with no spill, and its speed is sensitive to
+// its code shape well beyond what the source suggests (measured: a 32-bit instead of a 64-bit chunk window,
+// or one more shared-memory store in the refill branch, each cost 3-4 % of the launch): re-measure after any edit.
 //
 // Requires the configuration the bench uses: 32-bit indices, row descriptors, the edge hash set and
-// colrev (col joined with the reverse positions); fewer than 2^32 - 256 walks, walk_length < 65536.
+// colrev (col joined with the reverse positions); fewer than 2^32 walks, walk_length < 65536.
 #pragma once
 #include "walk_kernels.cuh"
 
@@ -44,27 +36,26 @@ enum : int {
 };
 enum : int { PS_IDLE = 0, PS_START, PS_ROW, PS_ACCEPTED, PS_ATTEMPT, PS_HASH };
 
-template <bool HAS_EOUT, bool HOST, int SLOTS = kPoolSlots>
+template <bool HAS_EOUT, int HOST, int SLOTS = kPoolSlots>
 __global__ void __launch_bounds__(kBlock, 6) node2vec_pool_kernel(const Node2vecParams P) {
   static_assert(SLOTS % 32 == 0 && SLOTS >= 32 && SLOTS <= 96, "whole slots per lane, within static shared memory");
   __shared__ uint32_t pool[PF_COUNT][kWarpsPerBlock][SLOTS];
   __shared__ uint8_t sel[kWarpsPerBlock][SLOTS];
-  __shared__ int s_live[kWarpsPerBlock];  // drain phase: live slots per warp, written at a round boundary
-  __shared__ int s_dry;                   // some warp of this block found the launch-wide queue empty
   constexpr unsigned kFull = 0xffffffffu;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const unsigned lt = (1u << lane) - 1u;
   const L2Policy pol = make_policies(P.hints);
   const int32_t L = P.walk_length;
   const int64_t n = P.num_walks;
+  const int64_t n_chunks = (n + 31) / 32;
 #define FLD(f, s) pool[f][warp][s]
 
   auto put_node = [&](int64_t row, int32_t k, int64_t node) {
-    if (HOST) reinterpret_cast<int32_t*>(P.n_out)[row * ((int64_t)L + 1) + k] = (int32_t)node;
+    if (HOST == HOST_NARROW) reinterpret_cast<int32_t*>(P.n_out)[row * ((int64_t)L + 1) + k] = (int32_t)node;
     else st8(P.n_out + row * ((int64_t)L + 1) + k, node, pol.stream);
   };
   auto put_edge = [&](int64_t row, int32_t k, int64_t edge) {
-    if (HOST) reinterpret_cast<int32_t*>(P.e_out)[row * (int64_t)L + k] = (int32_t)edge;
+    if (HOST == HOST_NARROW) reinterpret_cast<int32_t*>(P.e_out)[row * (int64_t)L + k] = (int32_t)edge;
     else P.e_out[row * (int64_t)L + k] = edge;
   };
   // a finished walk's rows are made visible, then counted for its slab (host single-launch mode)
@@ -82,118 +73,47 @@ __global__ void __launch_bounds__(kBlock, 6) node2vec_pool_kernel(const Node2vec
   constexpr int K = SLOTS / 32;  // slots per lane: slot lane + 32 k, k < K
 #pragma unroll
   for (int k = 0; k < K; k++) FLD(PF_LS, lane + 32 * k) = PS_IDLE;
-  if (threadIdx.x == 0) s_dry = 0;
-  __syncthreads();
-  uint32_t q_next = 0, q_end = 0;  // current chunk of 32 walks of the launch-wide queue (fewer than 2^32 - 256 walks)
+  __syncwarp();
+  int64_t q_next = 0, q_end = 0;  // current chunk of 32 walks of the launch-wide queue
   bool drained = false;
-  int round_trips = 0;    // drain phase: trips left before the next round boundary
 
   while (true) {
-    // the queue is dry for the whole launch once any warp has seen it dry; a warp that learns it from
-    // the block's flag still hands out what is left of its own chunk below
-    if (P.drain && !drained && *(volatile int*)&s_dry) drained = true;
     int st[K];
 #pragma unroll
     for (int k = 0; k < K; k++) st[k] = (int)(FLD(PF_LS, lane + 32 * k) & 7u);
 
-    // ---- hand unassigned walks to idle slots: from the warp's current chunk, then from the launch-wide queue
+    // ---- hand unassigned walks to idle slots
     unsigned idle[K];
     int n_idle = 0;
 #pragma unroll
     for (int k = 0; k < K; k++) { idle[k] = __ballot_sync(kFull, st[k] == PS_IDLE); n_idle += __popc(idle[k]); }
-    if (n_idle && (!drained || q_next < q_end)) {
+    if (n_idle && !drained) {
       int rank[K], before = 0;
 #pragma unroll
       for (int k = 0; k < K; k++) { rank[k] = before + __popc(idle[k] & lt); before += __popc(idle[k]); }
       int given = 0;
       while (given < n_idle) {
         if (q_next >= q_end) {
-          if (drained) break;
           unsigned long long chunk = 0;
           if (lane == 0) chunk = atomicAdd(P.queue, 1ull);
           chunk = __shfl_sync(kFull, chunk, 0);
-          if ((int64_t)chunk >= (n + 31) / 32) {
-            drained = true;
-            if (P.drain && lane == 0) *(volatile int*)&s_dry = 1;  // the other warps of the block stop asking too
-            break;
-          }
-          q_next = (uint32_t)chunk * 32u;
-          q_end = (uint32_t)min((int64_t)q_next + 32, n);
+          if ((int64_t)chunk >= n_chunks) { drained = true; break; }
+          q_next = (int64_t)chunk * 32;
+          q_end = min(q_next + 32, n);
         }
         const int take = min((int)(q_end - q_next), n_idle - given);
 #pragma unroll
         for (int k = 0; k < K; k++) {
           if (st[k] == PS_IDLE && rank[k] >= given && rank[k] < given + take) {
-            FLD(PF_I, lane + 32 * k) = q_next + (uint32_t)(rank[k] - given);
+            FLD(PF_I, lane + 32 * k) = (uint32_t)(q_next + (rank[k] - given));
             FLD(PF_LS, lane + 32 * k) = PS_START;
             st[k] = PS_START;
           }
         }
-        q_next += (uint32_t)take;
+        q_next += take;
         given += take;
       }
       __syncwarp();
-    }
-    // From here on, either the warp's chunk is used up or it has no idle slot: a warp without live slots
-    // has nothing left to hand out either.
-
-    // ---- drain phase, round boundary: count the block's live slots, pack them into few warps
-    // (with P.drain set, a warp that knows the queue is dry runs in rounds of trips between block barriers)
-    const bool in_drain = P.drain && drained;
-    if (in_drain && round_trips <= 0) {
-      unsigned lv[K];
-      int mine = 0;
-#pragma unroll
-      for (int k = 0; k < K; k++) { lv[k] = __ballot_sync(kFull, st[k] != PS_IDLE); mine += __popc(lv[k]); }
-      if (lane == 0) s_live[warp] = mine;
-      __syncthreads();
-      int total = 0, before = 0, holders = 0;
-#pragma unroll
-      for (int w = 0; w < kWarpsPerBlock; w++) {
-        const int c = s_live[w];
-        total += c;
-        if (w < warp) before += c;
-        holders += c > 0 ? 1 : 0;
-      }
-      __syncthreads();  // every warp has read the counts before any warp writes the next round's
-      if (total == 0) break;  // the same for every warp of the block: all leave together
-      const int need = (total + SLOTS - 1) / SLOTS;
-      if ((P.drain & 1) && holders > need) {  // packing frees at least one warp
-        int dw[K], ds[K];
-        int r = before;
-#pragma unroll
-        for (int k = 0; k < K; k++) {
-          const int g = r + __popc(lv[k] & lt);
-          dw[k] = g / SLOTS;
-          ds[k] = g - dw[k] * SLOTS;
-          r += __popc(lv[k]);
-        }
-        constexpr int kBatch = 4;  // fields moved per pass: read by all, barrier, written by all
-        static_assert(PF_COUNT % kBatch == 0 && PF_LS == PF_COUNT - 1, "the state word moves in the last pass");
-#pragma unroll 1
-        for (int f0 = 0; f0 < PF_COUNT; f0 += kBatch) {
-          uint32_t val[kBatch][K];
-#pragma unroll
-          for (int f = 0; f < kBatch; f++)
-#pragma unroll
-            for (int k = 0; k < K; k++) val[f][k] = pool[f0 + f][warp][lane + 32 * k];
-          __syncthreads();
-          if (f0 + kBatch == PF_COUNT) {  // every slot idle before the packed state words land
-#pragma unroll
-            for (int k = 0; k < K; k++) FLD(PF_LS, lane + 32 * k) = PS_IDLE;
-            __syncthreads();
-          }
-#pragma unroll
-          for (int f = 0; f < kBatch; f++)
-#pragma unroll
-            for (int k = 0; k < K; k++)
-              if ((lv[k] >> lane) & 1u) pool[f0 + f][dw[k]][ds[k]] = val[f][k];
-          __syncthreads();
-        }
-#pragma unroll
-        for (int k = 0; k < K; k++) st[k] = (int)(FLD(PF_LS, lane + 32 * k) & 7u);
-      }
-      round_trips = P.drain_trips;
     }
 
     // ---- pick the class most slots are in
@@ -206,22 +126,15 @@ __global__ void __launch_bounds__(kBlock, 6) node2vec_pool_kernel(const Node2vec
       mR[k] = __ballot_sync(kFull, st[k] >= PS_START && st[k] <= PS_ACCEPTED);
       nA += __popc(mA[k]); nH += __popc(mH[k]); nR += __popc(mR[k]);
     }
-    if (nA + nH + nR == 0) {  // every slot idle, and the refill above found nothing
-      if (!P.drain) break;
-      round_trips = 0;  // drain phase: wait for the block at the next round boundary (slots may arrive there)
-      continue;
-    }
-    // a warp of the drain phase with at most 32 live slots serves all of them, each on its own path
-    // (cls 0: every live slot, each on the path of its own state)
+    if (nA + nH + nR == 0) break;  // every slot idle: the queue is drained (idle slots are refilled above otherwise)
     int cls;
-    if (in_drain && (P.drain & 2) && nA + nH + nR <= 32) cls = 0;
-    else if (nA >= nH && nA >= nR) cls = PS_ATTEMPT;
+    if (nA >= nH && nA >= nR) cls = PS_ATTEMPT;
     else if (nH >= nR) cls = PS_HASH;
     else cls = PS_ROW;
     int cnt = 0;
 #pragma unroll
     for (int k = 0; k < K; k++) {
-      const unsigned m = cls == 0 ? (mA[k] | mH[k] | mR[k]) : cls == PS_ATTEMPT ? mA[k] : (cls == PS_HASH ? mH[k] : mR[k]);
+      const unsigned m = cls == PS_ATTEMPT ? mA[k] : (cls == PS_HASH ? mH[k] : mR[k]);
       if ((m >> lane) & 1u) sel[warp][cnt + __popc(m & lt)] = (uint8_t)(lane + 32 * k);
       cnt += __popc(m);
     }
@@ -235,10 +148,6 @@ __global__ void __launch_bounds__(kBlock, 6) node2vec_pool_kernel(const Node2vec
       const int64_t i = (int64_t)FLD(PF_I, s);
       uint32_t ls = FLD(PF_LS, s);
       int32_t l = (int32_t)(ls >> 16);
-      if (cls == 0) {  // at most 32 slots: one round, so the warp-wide value is not needed again
-        const int own = (int)(ls & 7u);
-        cls = own == PS_ATTEMPT ? PS_ATTEMPT : own == PS_HASH ? PS_HASH : PS_ROW;
-      }
 
       if (cls == PS_ROW) {
         // -------- START / ACCEPTED, then the row fetch of the node the walk now stands on
@@ -397,7 +306,6 @@ __global__ void __launch_bounds__(kBlock, 6) node2vec_pool_kernel(const Node2vec
       }
     }
     __syncwarp();
-    round_trips--;  // only read in the drain phase
   }
 #undef FLD
 }

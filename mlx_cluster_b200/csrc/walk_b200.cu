@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <chrono>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -70,15 +71,13 @@ struct Tuning {
   std::atomic<int32_t> n2v_rev{1};          // 1 auto (reverse positions when they pay), 0 never, 2 whenever available
   std::atomic<int32_t> n2v_pool{1};         // 1: pooled kernel (walk state in shared memory, one state class per trip)
   std::atomic<int32_t> n2v_blocks_per_sm{0};  // 0 = what the occupancy calculator allows
-  std::atomic<int32_t> n2v_drain{3};        // pooled kernel, once the queue is dry: bit 0 pack the block's live slots
-                                            // into few warps, bit 1 warps with <= 32 live slots serve all of them
-  std::atomic<int32_t> n2v_drain_trips{8};  // ... trips between two packing rounds
   std::atomic<int32_t> n2v_max_attempts{(int32_t)WALK_B200_MAX_ATTEMPTS};  // rejections after which a step gives up
   std::atomic<int32_t> l2_hints{3};         // bit 0: evict-last row bounds, bit 1: evict-first streams
   std::atomic<int32_t> l2_fetch_granularity{0};  // set only through walk_b200_set_tuning (applies the CUDA limit)
   std::atomic<int32_t> host_slab_mb{256};   // walk-matrix bytes per pipeline slab of the host entry points
   std::atomic<int32_t> use_rowdesc{1};      // host entry points: build and use the packed row descriptor
-  std::atomic<int32_t> host_narrow{1};      // host entry points: ids that fit int32 cross PCIe as int32
+  std::atomic<int32_t> host_narrow{2};      // host entry points: 1 ids that fit int32 cross PCIe as int32, 0 never,
+                                            // 2 whichever a short measurement at graph creation finds faster
   std::atomic<int32_t> host_threads{0};     // host threads that widen them again; 0 = min(16, hardware threads)
   std::atomic<int32_t> host_single_launch{1};  // node2vec host entry: one launch over all rows, slabs copied out
                                                // behind it as they complete (needs host_narrow)
@@ -97,8 +96,6 @@ std::atomic<int32_t>* tuning_slot(const char* key) {
   if (!strcmp(key, "n2v_batch_trips")) return &g_tuning.n2v_batch_trips;
   if (!strcmp(key, "n2v_draw_loop")) return &g_tuning.n2v_draw_loop;
   if (!strcmp(key, "n2v_blocks_per_sm")) return &g_tuning.n2v_blocks_per_sm;
-  if (!strcmp(key, "n2v_drain")) return &g_tuning.n2v_drain;
-  if (!strcmp(key, "n2v_drain_trips")) return &g_tuning.n2v_drain_trips;
   if (!strcmp(key, "n2v_max_attempts")) return &g_tuning.n2v_max_attempts;
   if (!strcmp(key, "l2_hints")) return &g_tuning.l2_hints;
   if (!strcmp(key, "l2_fetch_granularity")) return &g_tuning.l2_fetch_granularity;
@@ -328,7 +325,7 @@ bool pool_applies(const Node2vecParams& P, int member) {
   const int mode = g_tuning.n2v_pool.load();
   return mode != 0 && (mode == 2 || rev_pays(P)) && member == MEMBER_HASH && P.colrev && P.desc && !P.counters &&
          P.num_nodes <= 0x7fffffffll && P.num_edges < 0xfffffffell && P.edgeset_buckets < 0xffffffffull &&
-         P.num_walks < 0xffffff00ll && P.walk_length < 65536 && g_tuning.n2v_idx.load() != 1 &&
+         P.num_walks < 0xffffffffll && P.walk_length < 65536 && g_tuning.n2v_idx.load() != 1 &&
          g_tuning.n2v_rev.load() != 0;
 }
 
@@ -354,36 +351,41 @@ int launch_n2v(const Node2vecParams& P, bool sym, cudaStream_t s) {
   return launch_n2v_i<int64_t>(P, member, s);
 }
 
-// Single-launch mode of the host entry point: kernels that write int32 matrices and report finished
-// slabs. Built for 32-bit indices with row descriptors; returns kNoHostKernel for any other
-// configuration (the caller then runs the slab pipeline).
+// Single-launch mode of the host entry point: kernels that report finished slabs and write int32 matrices
+// (narrow transport) or int64 ones (wide). Built for 32-bit indices with row descriptors; returns
+// kNoHostKernel for any other configuration (the caller then runs the slab pipeline).
 constexpr int kNoHostKernel = -1;
 
-int launch_n2v_host(const Node2vecParams& P, bool sym, cudaStream_t s) {
+template <int HOST>
+int launch_n2v_host_t(const Node2vecParams& P, bool sym, cudaStream_t s) {
   const bool fits32 = P.num_nodes <= 0x7fffffffll && P.num_edges < 0x7fffffffll;
   if (!fits32 || !P.desc || P.counters || g_tuning.n2v_idx.load() == 1) return kNoHostKernel;
   const bool e = P.e_out != nullptr;
   int member = sym ? MEMBER_SEARCH_PREV : MEMBER_SEARCH_CAND;
   if (P.edgeset && P.edgeset_buckets > 0 && g_tuning.n2v_member.load() != 1) member = MEMBER_HASH;
   if (pool_applies(P, member)) {
-    if (e) return launch_n2v_kernel(node2vec_pool_kernel<true, true>, P, s, "node2vec_pool_kernel");
-    return launch_n2v_kernel(node2vec_pool_kernel<false, true>, P, s, "node2vec_pool_kernel");
+    if (e) return launch_n2v_kernel(node2vec_pool_kernel<true, HOST>, P, s, "node2vec_pool_kernel");
+    return launch_n2v_kernel(node2vec_pool_kernel<false, HOST>, P, s, "node2vec_pool_kernel");
   }
   if (member == MEMBER_HASH && P.colrev && rev_pays(P)) {
-    if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, true, false, true, true>, P, s);
-    return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, false, false, true, true>, P, s);
+    if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, true, false, true, HOST>, P, s);
+    return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, false, false, true, HOST>, P, s);
   }
   switch (member) {
     case MEMBER_HASH:
-      if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, true, false, false, true>, P, s);
-      return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, false, false, false, true>, P, s);
+      if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, true, false, false, HOST>, P, s);
+      return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_HASH, true, false, false, false, HOST>, P, s);
     case MEMBER_SEARCH_PREV:
-      if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_SEARCH_PREV, true, true, false, false, true>, P, s);
-      return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_SEARCH_PREV, true, false, false, false, true>, P, s);
+      if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_SEARCH_PREV, true, true, false, false, HOST>, P, s);
+      return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_SEARCH_PREV, true, false, false, false, HOST>, P, s);
     default:
-      if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_SEARCH_CAND, true, true, false, false, true>, P, s);
-      return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_SEARCH_CAND, true, false, false, false, true>, P, s);
+      if (e) return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_SEARCH_CAND, true, true, false, false, HOST>, P, s);
+      return launch_n2v_kernel(node2vec_walk_kernel<uint32_t, MEMBER_SEARCH_CAND, true, false, false, false, HOST>, P, s);
   }
+}
+
+int launch_n2v_host(const Node2vecParams& P, bool sym, bool narrow, cudaStream_t s) {
+  return narrow ? launch_n2v_host_t<HOST_NARROW>(P, sym, s) : launch_n2v_host_t<HOST_WIDE>(P, sym, s);
 }
 
 // Argument checks and kernel parameters shared by the device-pointer entry and the host entry.
@@ -408,9 +410,6 @@ int prepare_n2v(const walk_b200_csr* g, const int64_t* start, int64_t num_walks,
     const int32_t cap = g_tuning.n2v_max_attempts.load();
     P.max_attempts = cap < 1 ? 1u : (uint32_t)cap > WALK_B200_MAX_ATTEMPTS ? WALK_B200_MAX_ATTEMPTS : (uint32_t)cap;
   }
-  P.drain = g_tuning.n2v_drain.load() & 3;
-  P.drain_trips = g_tuning.n2v_drain_trips.load();
-  if (P.drain_trips < 1) P.drain_trips = 1;
   P.batch_lanes = g_tuning.n2v_batch_lanes.load();
   P.batch_trips = g_tuning.n2v_batch_trips.load();
   if (P.batch_lanes < 1) P.batch_lanes = 1;
@@ -995,6 +994,10 @@ struct walk_b200_graph {
   uint32_t* h_slab_flags = nullptr;
   size_t cap_start_all = 0, cap_all = 0, cap_eall = 0, cap_slab_done = 0, cap_slab_flags = 0;
   std::unique_ptr<WidenPool> pool;
+  // transport of the walk matrices to host buffers, measured once at creation (host_narrow = 2):
+  // pinned device-to-host copy rate and the widening threads' output rate, both in GB/s
+  bool prefer_narrow = true;
+  double measured_d2h_gbs = 0.0, measured_widen_gbs = 0.0;
   std::mutex mu;
 };
 
@@ -1080,23 +1083,34 @@ int flags_to_status(uint32_t f) {
               (f & WALK_B200_FLAG_EDGESET_FULL) ? " edge hash set overflow;" : "");
 }
 
-// node2vec over host buffers as ONE launch: all start rows go up, the kernel writes int32 matrices
-// that stay on the device, counts finished walks per slab of 2^shift rows and sets a flag in mapped
-// host memory when a slab is complete. The host copies each complete slab into pinned staging on a
-// second stream while the launch goes on, and widens it into the caller's int64 buffers. Against
-// one launch per slab this removes the drain at the end of every launch (each costs about as long
-// as the slowest walk of the slab; consecutive launches of a persistent kernel barely overlap).
-// The kernel never waits for the host. Returns kNoHostKernel (before doing anything) when this
-// mode does not apply; the caller then runs the slab pipeline. Called with g->mu held and the
-// graph's device current.
-int run_host_n2v_single(walk_b200_graph* g, const walk_b200_csr& csr, const int64_t* h_start, int64_t n, int32_t L,
-                        double p, double q, uint64_t seed, uint64_t base, uint64_t stride, int64_t* h_n_out,
+// Which transport a call uses for matrices whose ids fit 31 bits: the tuning decides, or (host_narrow = 2)
+// the measurement taken when the graph was created.
+bool use_narrow(const walk_b200_graph* g, bool ids_fit) {
+  const int mode = g_tuning.host_narrow.load();
+  if (!ids_fit || mode == 0) return false;
+  if (mode == 1) return true;
+  return g->prefer_narrow;
+}
+
+// node2vec over host buffers as ONE launch: all start rows go up, the kernel writes matrices that stay on
+// the device, counts finished walks per slab of 2^shift rows and sets a flag in mapped host memory when a
+// slab is complete. The host copies each complete slab out on a second stream while the launch goes on.
+// Narrow transport: the matrices are int32, a slab lands in pinned staging and host threads widen it into
+// the caller's int64 buffers. Wide transport: the matrices are int64 and a slab is copied straight into the
+// caller's buffers (pinned ones, or the copy does not overlap). Against one launch per slab this removes the
+// drain at the end of every launch (each costs about as long as the slowest walk of the slab; consecutive
+// launches of a persistent kernel barely overlap). The kernel never waits for the host. Returns
+// kNoHostKernel (before doing anything) when this mode does not apply; the caller then runs the slab
+// pipeline. Called with g->mu held and the graph's device current.
+int run_host_n2v_single(walk_b200_graph* g, const walk_b200_csr& csr, bool narrow, const int64_t* h_start, int64_t n,
+                        int32_t L, double p, double q, uint64_t seed, uint64_t base, uint64_t stride, int64_t* h_n_out,
                         int64_t* h_e_out) {
   constexpr int kLanes = walk_b200_graph::kLanes;
   const bool want_e = h_e_out && L > 0;
   if (!g->d_desc || g->num_nodes >= (1ll << 31) || g->num_edges >= (1ll << 31) - 1) return kNoHostKernel;
-  const size_t row32 = (size_t)(L + 1) * 4;
-  const size_t need = (size_t)n * row32 + (want_e ? (size_t)n * L * 4 : 0);
+  const size_t elem = narrow ? 4 : 8;
+  const size_t row_b = (size_t)(L + 1) * elem;
+  const size_t need = (size_t)n * row_b + (want_e ? (size_t)n * L * elem : 0);
   if (need > ((size_t)g_tuning.host_resident_mb.load() << 20)) return kNoHostKernel;
   if (g_tuning.n2v_idx.load() == 1) return kNoHostKernel;
   {  // the matrices must fit what the device has left (buffers kept from earlier calls count as free)
@@ -1106,17 +1120,17 @@ int run_host_n2v_single(walk_b200_graph* g, const walk_b200_csr& csr, const int6
     if (need + (size_t)n * 8 + ((size_t)64 << 20) > free_b + kept) return kNoHostKernel;
   }
 
-  // slab: the largest power of two of rows whose int32 copy is at most an eighth of the slab tuning
+  // slab: the largest power of two of rows whose copy is at most an eighth of the slab tuning
   // (small slabs keep the staging copy cache-warm for the widening threads and shorten the exposed tail)
   int shift = 10;
-  const size_t target = ((size_t)g_tuning.host_slab_mb.load() << 20) / 8;
-  while (shift < 30 && ((size_t)2 << shift) * row32 <= target) shift++;
+  const size_t target = ((size_t)g_tuning.host_slab_mb.load() << 20) / 8 * (narrow ? 1 : 2);
+  while (shift < 30 && ((size_t)2 << shift) * row_b <= target) shift++;
   const int64_t slab_rows = (int64_t)1 << shift;
   const int64_t slabs = (n + slab_rows - 1) / slab_rows;
 
   if (int rc = grow_one(&g->d_start_all, &g->cap_start_all, (size_t)n * 8)) return rc;
-  if (int rc = grow_one(&g->d_all, &g->cap_all, (size_t)n * row32)) return rc;
-  if (want_e) if (int rc = grow_one(&g->d_eall, &g->cap_eall, (size_t)n * L * 4)) return rc;
+  if (int rc = grow_one(&g->d_all, &g->cap_all, (size_t)n * row_b)) return rc;
+  if (want_e) if (int rc = grow_one(&g->d_eall, &g->cap_eall, (size_t)n * L * elem)) return rc;
   if (int rc = grow_one(&g->d_slab_done, &g->cap_slab_done, (size_t)slabs * 4)) return rc;
   if ((size_t)slabs * 4 > g->cap_slab_flags) {
     if (g->h_slab_flags) cudaFreeHost(g->h_slab_flags);
@@ -1125,10 +1139,12 @@ int run_host_n2v_single(walk_b200_graph* g, const walk_b200_csr& csr, const int6
     CUDA_TRY(cudaHostAlloc((void**)&g->h_slab_flags, (size_t)slabs * 4, cudaHostAllocMapped));
     g->cap_slab_flags = (size_t)slabs * 4;
   }
-  const size_t slab_bytes = (size_t)(slab_rows < n ? slab_rows : n) * row32;
-  if (int rc = grow_pinned(g->h_pack, &g->cap_hpack, slab_bytes)) return rc;
-  if (want_e) if (int rc = grow_pinned(g->h_epack, &g->cap_hepack, (size_t)(slab_rows < n ? slab_rows : n) * L * 4)) return rc;
-  if (int rc = ensure_pool(g)) return rc;
+  if (narrow) {
+    const size_t slab_bytes = (size_t)(slab_rows < n ? slab_rows : n) * row_b;
+    if (int rc = grow_pinned(g->h_pack, &g->cap_hpack, slab_bytes)) return rc;
+    if (want_e) if (int rc = grow_pinned(g->h_epack, &g->cap_hepack, (size_t)(slab_rows < n ? slab_rows : n) * L * 4)) return rc;
+    if (int rc = ensure_pool(g)) return rc;
+  }
   uint32_t* d_slab_flags = nullptr;
   CUDA_TRY(cudaHostGetDevicePointer((void**)&d_slab_flags, g->h_slab_flags, 0));
 
@@ -1151,7 +1167,7 @@ int run_host_n2v_single(walk_b200_graph* g, const walk_b200_csr& csr, const int6
   P.slab_done = g->d_slab_done;
   P.slab_flags = d_slab_flags;
   {
-    const int rc = launch_n2v_host(P, (csr.flags & WALK_B200_CSR_SYMMETRIC) != 0, work);
+    const int rc = launch_n2v_host(P, (csr.flags & WALK_B200_CSR_SYMMETRIC) != 0, narrow, work);
     if (rc == kNoHostKernel) {  // nothing was launched; leave the stream idle for the fallback
       CUDA_TRY(cudaStreamSynchronize(work));
       return kNoHostKernel;
@@ -1180,17 +1196,26 @@ int run_host_n2v_single(walk_b200_graph* g, const walk_b200_csr& csr, const int6
       }
       std::this_thread::yield();
     }
-    const int lane = (int)(k % kLanes);
-    // the lane's staging was widened kLanes - 1 slabs ago (the widen below trails by one slab)
-    CUDA_TRY(cudaMemcpyAsync(g->h_pack[lane], g->d_all + k * slab_rows * (L + 1), (size_t)rows_of(k) * row32,
-                             cudaMemcpyDeviceToHost, copy));
-    if (want_e)
-      CUDA_TRY(cudaMemcpyAsync(g->h_epack[lane], g->d_eall + k * slab_rows * L, (size_t)rows_of(k) * L * 4,
+    if (narrow) {
+      const int lane = (int)(k % kLanes);
+      // the lane's staging was widened kLanes - 1 slabs ago (the widen below trails by one slab)
+      CUDA_TRY(cudaMemcpyAsync(g->h_pack[lane], g->d_all + k * slab_rows * (L + 1), (size_t)rows_of(k) * row_b,
                                cudaMemcpyDeviceToHost, copy));
-    CUDA_TRY(cudaEventRecord(g->landed[lane], copy));
-    if (k >= 1) if (int rc = widen(k - 1)) return rc;
+      if (want_e)
+        CUDA_TRY(cudaMemcpyAsync(g->h_epack[lane], g->d_eall + k * slab_rows * L, (size_t)rows_of(k) * L * 4,
+                                 cudaMemcpyDeviceToHost, copy));
+      CUDA_TRY(cudaEventRecord(g->landed[lane], copy));
+      if (k >= 1) if (int rc = widen(k - 1)) return rc;
+    } else {
+      const int64_t* d_all64 = reinterpret_cast<const int64_t*>(g->d_all);
+      CUDA_TRY(cudaMemcpyAsync(h_n_out + k * slab_rows * (L + 1), d_all64 + k * slab_rows * (L + 1),
+                               (size_t)rows_of(k) * row_b, cudaMemcpyDeviceToHost, copy));
+      if (want_e)
+        CUDA_TRY(cudaMemcpyAsync(h_e_out + k * slab_rows * L, reinterpret_cast<const int64_t*>(g->d_eall) + k * slab_rows * L,
+                                 (size_t)rows_of(k) * L * 8, cudaMemcpyDeviceToHost, copy));
+    }
   }
-  if (int rc = widen(slabs - 1)) return rc;
+  if (narrow) if (int rc = widen(slabs - 1)) return rc;
   CUDA_TRY(cudaStreamSynchronize(work));
   CUDA_TRY(cudaStreamSynchronize(copy));
   uint32_t f = 0;
@@ -1222,8 +1247,7 @@ int run_host_walk(walk_b200_graph* g, bool biased, const int64_t* h_start, const
 
   constexpr int kLanes = walk_b200_graph::kLanes;
   const bool want_e = h_e_out && L > 0;
-  const bool narrow = g_tuning.host_narrow.load() != 0 && g->num_nodes < (1ll << 31) &&
-                      (!want_e || g->num_edges < (1ll << 31));
+  const bool narrow = use_narrow(g, g->num_nodes < (1ll << 31) && (!want_e || g->num_edges < (1ll << 31)));
   walk_b200_csr csr{};
   csr.rowptr = g->d_rowptr; csr.col = g->d_col; csr.num_nodes = g->num_nodes; csr.num_edges = g->num_edges;
   csr.rowdesc = g->d_desc; csr.flags = g->csr_flags;
@@ -1231,8 +1255,8 @@ int run_host_walk(walk_b200_graph* g, bool biased, const int64_t* h_start, const
   csr.colrev = g->d_colrev;
   csr.fused = g->d_fused;
 
-  if (biased && narrow && g_tuning.host_single_launch.load() != 0) {
-    const int rc = run_host_n2v_single(g, csr, h_start, n, L, p, q, seed, base, stride, h_n_out, h_e_out);
+  if (biased && g_tuning.host_single_launch.load() != 0) {
+    const int rc = run_host_n2v_single(g, csr, narrow, h_start, n, L, p, q, seed, base, stride, h_n_out, h_e_out);
     if (rc != kNoHostKernel) return rc;
   }
 
@@ -1310,6 +1334,67 @@ int run_host_walk(walk_b200_graph* g, bool biased, const int64_t* h_start, const
   uint32_t f = 0;
   CUDA_TRY(cudaMemcpy(&f, g->d_flags, sizeof(f), cudaMemcpyDeviceToHost));
   return flags_to_status(f);
+}
+
+// Which transport serves this process best is a property of the box and of what else runs on it (the ranks of
+// one machine share its host memory): time a pinned device-to-host copy and the widening of as many elements,
+// once, at graph creation, when every rank of a job is doing the same. Per byte of int64 output the narrow
+// transport costs max(half a byte over the bus, one byte through the widening threads), the wide one a byte
+// over the bus.
+int measure_transport(walk_b200_graph* g) {
+  const size_t elems = (size_t)8 << 20;  // 32 MiB of int32, 64 MiB of int64
+  int32_t* h32 = nullptr;
+  int64_t* h64 = nullptr;
+  int64_t* d64 = nullptr;
+  int rc = WALK_B200_OK;
+  cudaEvent_t e0 = nullptr, e1 = nullptr;
+  auto cleanup = [&]() {
+    if (h32) cudaFreeHost(h32);
+    if (h64) cudaFreeHost(h64);
+    if (d64) cudaFree(d64);
+    if (e0) cudaEventDestroy(e0);
+    if (e1) cudaEventDestroy(e1);
+  };
+#define M_TRY(expr)                                                                                  \
+  do {                                                                                               \
+    cudaError_t err__ = (expr);                                                                      \
+    if (err__ != cudaSuccess) {                                                                      \
+      rc = fail(WALK_B200_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(err__));              \
+      cleanup();                                                                                     \
+      return rc;                                                                                     \
+    }                                                                                                \
+  } while (0)
+  M_TRY(cudaHostAlloc((void**)&h32, elems * 4, cudaHostAllocDefault));
+  M_TRY(cudaHostAlloc((void**)&h64, elems * 8, cudaHostAllocDefault));
+  M_TRY(cudaMalloc((void**)&d64, elems * 8));
+  M_TRY(cudaEventCreate(&e0));
+  M_TRY(cudaEventCreate(&e1));
+  cudaStream_t s = g->streams[0];
+  M_TRY(cudaMemsetAsync(d64, 0, elems * 8, s));
+  M_TRY(cudaMemcpyAsync(h64, d64, elems * 8, cudaMemcpyDeviceToHost, s));  // warm-up, touches the pages
+  M_TRY(cudaEventRecord(e0, s));
+  const int reps = 4;
+  for (int r = 0; r < reps; r++) M_TRY(cudaMemcpyAsync(h64, d64, elems * 8, cudaMemcpyDeviceToHost, s));
+  M_TRY(cudaEventRecord(e1, s));
+  M_TRY(cudaEventSynchronize(e1));
+  float ms = 0.f;
+  M_TRY(cudaEventElapsedTime(&ms, e0, e1));
+#undef M_TRY
+  if ((rc = ensure_pool(g))) { cleanup(); return rc; }
+  memset(h32, 1, elems * 4);
+  g->pool->widen(h32, h64, (int64_t)elems);
+  const auto t0 = std::chrono::steady_clock::now();
+  for (int r = 0; r < reps; r++) g->pool->widen(h32, h64, (int64_t)elems);
+  const double wsecs = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+  cleanup();
+  g->measured_d2h_gbs = ms > 0.f ? (double)reps * elems * 8 / (ms * 1e-3) / 1e9 : 0.0;
+  g->measured_widen_gbs = wsecs > 0 ? (double)reps * elems * 8 / wsecs / 1e9 : 0.0;
+  if (g->measured_d2h_gbs > 0 && g->measured_widen_gbs > 0) {
+    const double narrow_cost = std::fmax(0.5 / g->measured_d2h_gbs, 1.0 / g->measured_widen_gbs);
+    const double wide_cost = 1.0 / g->measured_d2h_gbs;
+    g->prefer_narrow = narrow_cost * 1.1 < wide_cost;
+  }
+  return WALK_B200_OK;
 }
 
 }  // namespace
@@ -1404,7 +1489,42 @@ int walk_b200_graph_create(const int64_t* h_rowptr, const int64_t* h_col, int64_
   }
   G_TRY(cudaStreamSynchronize(s));
 #undef G_TRY
+  if (g_tuning.host_narrow.load() == 2 && num_nodes < (1ll << 31)) {
+    if (int rc = measure_transport(g)) return bail(rc);
+  }
   *out = g;
+  return WALK_B200_OK;
+}
+
+int walk_b200_graph_host_transport(const walk_b200_graph* g, int32_t* narrow, double* d2h_gbs, double* widen_gbs) {
+  if (!g) return fail(WALK_B200_ERR_INVALID_ARG, "graph is NULL");
+  if (narrow) *narrow = use_narrow(g, g->num_nodes < (1ll << 31)) ? 1 : 0;
+  if (d2h_gbs) *d2h_gbs = g->measured_d2h_gbs;
+  if (widen_gbs) *widen_gbs = g->measured_widen_gbs;
+  return WALK_B200_OK;
+}
+
+int walk_b200_host_widen_probe(size_t out_bytes, double* out_gbs) {
+  if (!out_gbs || out_bytes < (1u << 20)) return fail(WALK_B200_ERR_INVALID_ARG, "widen probe needs at least 1 MiB and a result");
+  *out_gbs = 0.0;
+  int threads = g_tuning.host_threads.load();
+  if (threads <= 0) {
+    threads = (int)std::thread::hardware_concurrency();
+    if (threads > 16) threads = 16;
+    if (threads < 1) threads = 1;
+  }
+  const int64_t count = (int64_t)(out_bytes / 8);
+  std::unique_ptr<int32_t[]> src(new (std::nothrow) int32_t[count]);
+  std::unique_ptr<int64_t[]> dst(new (std::nothrow) int64_t[count]);
+  if (!src || !dst) return fail(WALK_B200_ERR_INVALID_ARG, "out of host memory");
+  memset(src.get(), 1, (size_t)count * 4);
+  WidenPool pool(threads - 1);
+  pool.widen(src.get(), dst.get(), count);  // touches the pages
+  const auto t0 = std::chrono::steady_clock::now();
+  const int reps = 3;
+  for (int r = 0; r < reps; r++) pool.widen(src.get(), dst.get(), count);
+  const double secs = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+  if (secs > 0) *out_gbs = (double)reps * (double)count * 8.0 / secs / 1e9;
   return WALK_B200_OK;
 }
 

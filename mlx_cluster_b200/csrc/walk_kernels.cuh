@@ -593,13 +593,12 @@ struct Node2vecParams {
   uint32_t max_attempts;
   int32_t batch_lanes, batch_trips;  // batching of the rare state paths (see the kernel)
   int32_t draw_loop;                 // REV: memory-free rejections consumed per trip
-  int32_t drain, drain_trips;        // pooled kernel: drain phase (bit 0 pack slots, bit 1 serve all), trips per round
   int64_t* n_out;
   int64_t* e_out;
   uint32_t* flags;
   unsigned long long* counters;
   unsigned long long* queue;  // launch-wide chunk counter, zero at launch
-  // HOST kernels only: n_out / e_out point at int32 matrices; finished walks are counted per slab of
+  // HOST kernels only (HOST_NARROW: n_out / e_out point at int32 matrices): finished walks are counted per slab of
   // 2^slab_shift consecutive rows in slab_done (zero at launch); the walk that completes a slab sets
   // slab_flags[slab] (mapped host memory), after which the host may copy that slab's rows out while
   // the launch goes on.
@@ -610,6 +609,10 @@ struct Node2vecParams {
 
 enum : int { ST_IDLE = 0, ST_START, ST_ROW, ST_ACCEPTED, ST_ATTEMPT, ST_XROW, ST_SEARCH, ST_HASH };
 enum : int { MEMBER_SEARCH_PREV = 0, MEMBER_SEARCH_CAND = 1, MEMBER_HASH = 2 };
+// HOST template argument of the node2vec kernels: the single-launch mode of the host-buffer entry point.
+// HOST_NARROW: the matrices are int32 (ids fit; half the bytes cross the bus, host threads widen them);
+// HOST_WIDE: int64, copied straight into the caller's buffer. Both count finished walks per slab.
+enum : int { HOST_NONE = 0, HOST_NARROW = 1, HOST_WIDE = 2 };
 
 // Persistent warps; one walk per lane; one gather per loop trip whatever the lane is doing.
 //   ST_START     fetch the start node of a freshly assigned walk
@@ -649,10 +652,10 @@ enum : int { MEMBER_SEARCH_PREV = 0, MEMBER_SEARCH_CAND = 1, MEMBER_HASH = 2 };
 // rejected without touching memory at all. At (p, q) = (0.25, 4) that is three attempts in four.
 // Same draws, same decisions, fewer gathers.
 //
-// HOST (the host-buffer entry point's single-launch mode): the walk and edge matrices are int32
-// (P.n_out / P.e_out point at int32 storage; the ids fit) and finished walks are counted per slab of
-// 2^slab_shift rows, so the host can copy a slab out as soon as its last walk is done.
-template <typename idx_t, int MEMBER, bool USE_DESC, bool HAS_EOUT, bool COUNT, bool REV = false, bool HOST = false>
+// HOST (the host-buffer entry point's single-launch mode): finished walks are counted per slab of
+// 2^slab_shift rows, so the host can copy a slab out as soon as its last walk is done; with HOST_NARROW
+// the walk and edge matrices are int32 (P.n_out / P.e_out point at int32 storage; the ids fit).
+template <typename idx_t, int MEMBER, bool USE_DESC, bool HAS_EOUT, bool COUNT, bool REV = false, int HOST = HOST_NONE>
 __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(const Node2vecParams P) {
   static_assert(!REV || (MEMBER == MEMBER_HASH && USE_DESC && sizeof(idx_t) == 4), "REV needs hash membership, row descriptors, 32-bit indices");
   constexpr unsigned kFull = 0xffffffffu;
@@ -689,11 +692,11 @@ __global__ void __launch_bounds__(kBlock, COUNT ? 1 : 6) node2vec_walk_kernel(co
   bool finished = false;          // the lane completed a walk in the last trip (progress reporting)
 
   auto put_node = [&](int64_t row, int32_t k, int64_t node) {
-    if (HOST) reinterpret_cast<int32_t*>(P.n_out)[row * ((int64_t)L + 1) + k] = (int32_t)node;
+    if (HOST == HOST_NARROW) reinterpret_cast<int32_t*>(P.n_out)[row * ((int64_t)L + 1) + k] = (int32_t)node;
     else st8(P.n_out + row * ((int64_t)L + 1) + k, node, pol.stream);
   };
   auto put_edge = [&](int64_t row, int32_t k, int64_t edge) {
-    if (HOST) reinterpret_cast<int32_t*>(P.e_out)[row * (int64_t)L + k] = (int32_t)edge;
+    if (HOST == HOST_NARROW) reinterpret_cast<int32_t*>(P.e_out)[row * (int64_t)L + k] = (int32_t)edge;
     else P.e_out[row * (int64_t)L + k] = edge;
   };
 

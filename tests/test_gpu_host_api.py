@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 def _reset():
     yield
     _lib.set_tuning("host_slab_mb", 256)
-    _lib.set_tuning("host_narrow", 1)
+    _lib.set_tuning("host_narrow", 2)
     _lib.set_tuning("host_threads", 0)
     _lib.set_tuning("host_single_launch", 1)
     _lib.set_tuning("n2v_pool", 1)
@@ -80,8 +80,11 @@ def test_narrow_transport_is_invisible(cuda):
     assert (want_e == -1).any()
     want_b, want_be = oracle.node2vec_walk(rowptr.numpy(), col.numpy(), start_np, L, 0.25, 4.0, seed=3,
                                            return_edges=True)
+    # narrow: 1 int32 on the bus, 0 int64 straight into the caller's buffer, 2 whichever the graph measured
     for narrow, threads, slab_mb, pinned, single in ((0, 0, 2, True, 1), (1, 1, 2, True, 0), (1, 3, 1, False, 1),
-                                                     (1, 0, 256, True, 1), (1, 5, 3, False, 0), (1, 2, 4, True, 1)):
+                                                     (1, 0, 256, True, 1), (1, 5, 3, False, 0), (1, 2, 4, True, 1),
+                                                     (0, 0, 2, True, 0), (0, 0, 1, False, 1), (2, 0, 2, True, 1),
+                                                     (2, 2, 256, False, 1)):
         _lib.set_tuning("host_narrow", narrow)
         _lib.set_tuning("host_single_launch", single)
         _lib.set_tuning("host_threads", threads)
@@ -104,6 +107,22 @@ def test_narrow_transport_is_invisible(cuda):
             out, e = rejection_sampling(rowptr, col, start, L, 0.25, 4.0, seed=3, edgeset=True, return_edges=True)
             np.testing.assert_array_equal(out.numpy(), want_b)
             np.testing.assert_array_equal(e.numpy(), want_be)
+
+
+def test_transport_choice_is_reported(cuda, golden):
+    g = golden
+    _lib.set_tuning("host_narrow", 2)
+    hg = HostGraph(g["rowptr1"], g["col1"])
+    d2h, widen = _lib.host_transport_rates(hg._h)
+    assert d2h > 0.5 and widen > 0.5          # GB/s, measured at creation
+    chosen = _lib.host_transport(hg._h)
+    assert chosen in (0, 1)
+    _lib.set_tuning("host_narrow", 0)
+    assert _lib.host_transport(hg._h) == 0
+    _lib.set_tuning("host_narrow", 1)
+    assert _lib.host_transport(hg._h) == 1
+    hg.close()
+    assert _lib.host_widen_probe(32 << 20) > 0.5
 
 
 def test_host_entry_reports_bad_input(cuda, golden):

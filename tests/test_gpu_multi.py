@@ -58,6 +58,22 @@ def _worker(rank, world, port, q):
                 ok = ok and full is not None and np.array_equal(full.cpu().numpy(), want)
             else:
                 ok = ok and full is None
+        # a caller-chosen row range of the block layout, received in place on rank 0
+        shard, (b, e) = sharding.sharded_walk(biased_block, start, L, layout="block")
+        for lo, hi in ((0, 30001), (9000, 22000), (b, e) if rank == 0 else sharding.shard_range(30001, world, 0)):
+            part = sharding.gather_rows(shard, 30001, row_range=(lo, hi), chunk_rows=4096)
+            if rank == 0:
+                ok = ok and part is not None and np.array_equal(part.cpu().numpy(), want_b[lo:hi])
+            else:
+                ok = ok and part is None
+        # one process driving both devices through the operator's own keywords
+        if rank == 0:
+            blocks = rejection_sampling(rowptr.to(dev), col.to(dev), start, L, 0.25, 4.0, seed=5, devices=[0, 1])
+            ok = ok and [t.device.index for t in blocks] == [0, 1]
+            ok = ok and np.array_equal(np.concatenate([t.cpu().numpy() for t in blocks]), want_b)
+            full = random_walk(rowptr.to(dev), col.to(dev), start, rand, L, devices=[1, 0], gather=True)
+            ok = ok and full.device == dev and np.array_equal(full.cpu().numpy(), want_u)
+        dist.barrier()
         q.put((rank, bool(ok)))
     finally:
         dist.destroy_process_group()

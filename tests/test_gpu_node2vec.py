@@ -24,8 +24,6 @@ def _reset_tuning():
     _lib.set_tuning("n2v_rev", 1)
     _lib.set_tuning("n2v_pool", 1)
     _lib.set_tuning("l2_hints", 3)
-    _lib.set_tuning("n2v_drain", 3)
-    _lib.set_tuning("n2v_drain_trips", 8)
     _lib.set_tuning("n2v_max_attempts", 1 << 22)
 
 
@@ -310,18 +308,16 @@ def test_properties_at_scale(cuda):
     _lib.set_tuning("n2v_idx", 1)
     assert torch.equal(out, rejection_sampling(rowptr, col, start, L, 0.25, 4.0, seed=3, symmetric=True))
     assert torch.equal(out, rejection_sampling(None, None, start, L, 0.25, 4.0, graph=hashed, seed=3))
-    # every 997th row of the pooled kernel's matrix (with and without its drain phase) and of the per-lane
-    # kernel's against the CPU restatement, which is handed the same global walk indices 0, 997, ...
+    # every 997th row of the pooled kernel's matrix and of the per-lane kernel's against the CPU restatement,
+    # which is handed the same global walk indices 0, 997, ...
     rp_h, cl_h = rowptr.cpu().numpy(), col.cpu().numpy()
     picked = torch.arange(0, n_nodes, 997, device=cuda)
     want = oracle.node2vec_walk(rp_h, cl_h, picked.cpu().numpy(), L, 0.25, 4.0, seed=3, walk_index_stride=997)
     _lib.set_tuning("n2v_idx", 0)
-    for pool, drain, trips in ((2, 3, 8), (2, 0, 8), (2, 1, 1), (2, 2, 3), (2, 3, 64), (0, 0, 8)):
+    for pool in (2, 0):
         _lib.set_tuning("n2v_pool", pool)
-        _lib.set_tuning("n2v_drain", drain)
-        _lib.set_tuning("n2v_drain_trips", trips)
         got = rejection_sampling(None, None, start, L, 0.25, 4.0, graph=hashed, seed=3, check=True)
-        assert torch.equal(got, out), (pool, drain, trips)
+        assert torch.equal(got, out), pool
         np.testing.assert_array_equal(got[picked].cpu().numpy(), want)
     # a sub-sample of rows against the CPU restatement
     rows = torch.arange(0, n_nodes, 997, device=cuda)

@@ -7,7 +7,8 @@ trigger the device-wide synchronisation a driver allocation implies. For them
 (the packed row descriptors) in a fixed array inside the library. This test calls it
 through the C ABI twice in a row -- the second time on a different, smaller graph, so
 that descriptors left behind by the first call would show up if they were ever read --
-and requires bit-identical walks to the ordinary entry point. Collected last on purpose.
+and requires bit-identical walks to the ordinary entry point and to the CPU restatement of the
+reference loop. Collected last on purpose.
 """
 import ctypes as C
 
@@ -15,6 +16,7 @@ import numpy as np
 import pytest
 import torch
 
+import oracle
 from mlx_cluster_b200 import _lib, graphs
 
 pytestmark = pytest.mark.gpu
@@ -53,6 +55,11 @@ def _walk_both_ways(dev, rowptr, col, n_walks, L, seed):
     assert int(flags.item()) == 0 and int(flags2.item()) == 0
     assert torch.equal(got_n, want_n), "walk matrix differs from the ordinary entry point"
     assert torch.equal(got_e, want_e), "edge ids differ from the ordinary entry point"
+    # and against the checker itself, not only against another CUDA path
+    ref_n, ref_e = oracle.uniform_walk(rowptr.cpu().numpy(), col.cpu().numpy(), start.cpu().numpy(),
+                                       rand.cpu().numpy(), L, return_edges=True)
+    assert np.array_equal(got_n.cpu().numpy(), ref_n), "walk matrix differs from the CPU restatement"
+    assert np.array_equal(got_e.cpu().numpy(), ref_e), "edge ids differ from the CPU restatement"
     return mem_before, mem_after
 
 
