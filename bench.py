@@ -48,9 +48,9 @@ RMAT = dict(a=0.57, b=0.19, c=0.19, d=0.05)
 # which does not depend on the graph's size: every access misses to DRAM in both cases) times the random
 # accesses one launch of this run issues, counted in this run.
 NCU_SMALL_CASE = {
-    "node2vec": dict(workload="node2vec_rmat20", dram_bytes=19.60e9, accesses=3.4612e8,
+    "node2vec": dict(workload="node2vec_rmat20", dram_bytes=19.60e9, accesses=346134263,
                      source="profiles/node2vec_pool_kernel__node2vec_rmat20.md"),
-    "uniform": dict(workload="uniform_rmat20", dram_bytes=4.70e9, accesses=5.379e7,
+    "uniform": dict(workload="uniform_rmat20", dram_bytes=4.70e9, accesses=53816512,
                     source="profiles/uniform_walk_staged_kernel__uniform_rmat20.md"),
 }
 PHILOX_SEED = 20240607
@@ -486,7 +486,7 @@ def run_workload(args, name, wl, dev, world, rank, barrier, allmax, allsum, ligh
                                   "issues per GPU, counted in this run",
                 "kernel": "node2vec_pool_kernel (node2vec_walk_kernel where the pooled form does not apply)" if
                 wl["kind"] == "node2vec" else "uniform_walk_staged_kernel", "kernel_ms": kernel_ms,
-                "kernel_launched": _lib.last_kernel(),
+                "kernel_launched": _lib.last_kernel(), "random_accesses_per_launch": int(accesses),
                 "algorithmic_bytes_per_launch": alg_bytes, "gathered_bytes_per_launch": gathered_bytes,
                 "gathered_gbs": allsum(gathered_bytes / (kernel_ms * 1e-3) / 1e9) / world,
                 "algorithmic_bytes_per_walk_step": alg_bytes / max(1, rows * L)}

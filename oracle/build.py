@@ -5,9 +5,11 @@ Two shared objects come out of it:
 * ``oracle/libwalk_oracle.so`` -- the C restatement in ``walk_oracle.c`` (gcc).
 * ``oracle/_ref/libref_walk.so`` -- the reference's own ``RandomWalk.cpp`` and
   ``BiasedRandomWalk.cpp``, compiled unmodified from where the reference checkout
-  lies (``$WALK_REFERENCE_DIR``) against the header stand-ins in ``mlx_stub/``
-  plus ``ref_harness.cpp``. Only built when that checkout is present; the built
-  file is what travels to machines that have no checkout.
+  lies (``$WALK_REFERENCE_DIR``, else a directory ``reference`` beside this
+  repository) against the header stand-ins in ``mlx_stub/`` plus ``ref_harness.cpp``.
+  Only built when that checkout is present; the built file is what travels to
+  machines that have no checkout. ``python oracle/build.py --require-ref`` fails
+  with a message when neither the checkout nor a built library is there.
 
 Run as ``python oracle/build.py``.
 """
@@ -19,7 +21,7 @@ import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-REFERENCE_DIR = Path(os.environ.get("WALK_REFERENCE_DIR", "/root/reference"))
+REFERENCE_DIR = Path(os.environ.get("WALK_REFERENCE_DIR") or HERE.parent.parent / "reference")
 ORACLE_SO = HERE / "libwalk_oracle.so"
 REF_SO = HERE / "_ref" / "libref_walk.so"
 
@@ -66,6 +68,9 @@ def main() -> int:
     print("oracle:", build_oracle(force="--force" in sys.argv))
     ref = build_ref(force="--force" in sys.argv)
     print("reference build:", ref if ref else "skipped (no reference checkout)")
+    if ref is None and "--require-ref" in sys.argv:
+        print(f"no reference checkout at {REFERENCE_DIR} (set WALK_REFERENCE_DIR) and no built {REF_SO}", file=sys.stderr)
+        return 1
     return 0
 
 
