@@ -393,7 +393,8 @@ def run_workload(args, name, wl, dev, world, rank, barrier, allmax, allsum, ligh
     walks_timed = n_walks if shard_world == world else rows  # a lone rank's share counts only its own rows
     t_prep = time.perf_counter()
     graph = WalkGraph(rowptr, col, symmetric=True, edgeset=(wl["kind"] == "node2vec" and args.membership == "hash"),
-                      fused=(wl["kind"] == "uniform" and not args.no_fused))
+                      fused=(wl["kind"] == "uniform" and not args.no_fused),
+                      edgeset_slots_per_edge=args.edgeset_slots_per_edge)
     torch.cuda.synchronize(dev)
     prep_s = time.perf_counter() - t_prep
 
@@ -729,6 +730,9 @@ def main():
     ap.add_argument("--device-rand", action="store_true",
                     help="uniform walk: generate the draws in the kernel instead of reading a rand array")
     ap.add_argument("--no-fused", action="store_true", help="uniform walk: do not build fused edge records")
+    ap.add_argument("--edgeset-slots-per-edge", type=float, default=None,
+                    help="node2vec: size of the edge hash set (2 = half full, the library's minimum; 4 = a quarter full; "
+                         "default: the library's tuning, 4 when it fits)")
     ap.add_argument("--no-probe", action="store_true", help="skip the random-gather ceiling probe")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")

@@ -165,8 +165,10 @@ int walk_b200_rowdesc_pack(const int64_t* rowptr, int64_t num_nodes, int64_t num
  * Edge hash set: an exact set of all directed edges, so that node2vec's membership test
  * "is t a neighbour of x" (is_neighbor, random_walks/BiasedRandomWalk.cpp:20-28, a linear
  * scan there) costs about one 32-byte read instead of a binary search over col.
- * walk_b200_edgeset_buckets gives the table size for a graph (16 bytes per edge: load
- * factor 0.5); table is caller scratch of 32 * buckets bytes, 32-byte aligned. Needs
+ * walk_b200_edgeset_buckets gives the smallest table size for a graph (16 bytes per edge: load
+ * factor 0.5); any larger bucket count works too, and a sparser table answers more tests from
+ * their first bucket (measured on R-MAT 24 at p=0.25, q=4: 1.22 buckets read per test half full,
+ * 1.02 a quarter full, 4.5 % off the launch); table is caller scratch of 32 * buckets bytes, 32-byte aligned. Needs
  * num_nodes < 2^32 - 1 (else WALK_B200_ERR_UNSUPPORTED). Works for any CSR, directed or
  * not, sorted or not. Put the pointer and bucket count into walk_b200_csr.
  */
@@ -394,6 +396,8 @@ int walk_b200_gather_probe_ex(size_t array_bytes, int32_t iters, int32_t chains,
  *   uniform_variant, uniform_fused, l2_hints, l2_fetch_granularity, use_rowdesc
  *   n2v_idx, n2v_member, n2v_rev, n2v_pool (0 per-lane kernel, 1 pooled kernel where it wins, 2 always),
  *   n2v_batch_lanes, n2v_batch_trips, n2v_draw_loop, n2v_blocks_per_sm,
+ *   edgeset_slots_per_edge (size of the edge hash set a resident graph builds for itself, in 8-byte slots per
+ *   edge: 2 = half full, the minimum; default 4, taken when the table fits half of the free device memory),
  *   n2v_max_attempts (rejections after which a step gives up, at most WALK_B200_MAX_ATTEMPTS: the one key that
  *   can change a result, and only for steps that reach the cap, which raise WALK_B200_FLAG_ATTEMPT_CAP)
  *   host_slab_mb, host_narrow (1 int32 on the bus, 0 int64, 2 measured at graph creation), host_threads (widening threads, 0 = min(16, cores)),

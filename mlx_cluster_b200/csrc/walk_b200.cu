@@ -71,6 +71,8 @@ struct Tuning {
   std::atomic<int32_t> n2v_rev{1};          // 1 auto (reverse positions when they pay), 0 never, 2 whenever available
   std::atomic<int32_t> n2v_pool{1};         // 1: pooled kernel (walk state in shared memory, one state class per trip)
   std::atomic<int32_t> n2v_blocks_per_sm{0};  // 0 = what the occupancy calculator allows
+  std::atomic<int32_t> edgeset_slots_per_edge{4};  // size of the edge hash set a resident graph builds: 2 = half full
+                                                   // (the minimum), 4 = a quarter full (fewer second buckets read)
   std::atomic<int32_t> n2v_max_attempts{(int32_t)WALK_B200_MAX_ATTEMPTS};  // rejections after which a step gives up
   std::atomic<int32_t> l2_hints{3};         // bit 0: evict-last row bounds, bit 1: evict-first streams
   std::atomic<int32_t> l2_fetch_granularity{0};  // set only through walk_b200_set_tuning (applies the CUDA limit)
@@ -97,6 +99,7 @@ std::atomic<int32_t>* tuning_slot(const char* key) {
   if (!strcmp(key, "n2v_draw_loop")) return &g_tuning.n2v_draw_loop;
   if (!strcmp(key, "n2v_blocks_per_sm")) return &g_tuning.n2v_blocks_per_sm;
   if (!strcmp(key, "n2v_max_attempts")) return &g_tuning.n2v_max_attempts;
+  if (!strcmp(key, "edgeset_slots_per_edge")) return &g_tuning.edgeset_slots_per_edge;
   if (!strcmp(key, "l2_hints")) return &g_tuning.l2_hints;
   if (!strcmp(key, "l2_fetch_granularity")) return &g_tuning.l2_fetch_granularity;
   if (!strcmp(key, "host_slab_mb")) return &g_tuning.host_slab_mb;
@@ -1453,6 +1456,16 @@ int walk_b200_graph_create(const int64_t* h_rowptr, const int64_t* h_col, int64_
     walk_b200_csr csr{};
     csr.rowptr = g->d_rowptr; csr.col = g->d_col; csr.num_nodes = num_nodes; csr.num_edges = num_edges;
     if (int rc = walk_b200_edgeset_buckets(num_edges, &g->edgeset_buckets)) return bail(rc);
+    {  // a sparser table answers more membership tests from their first bucket; taken when it fits comfortably
+      int32_t spe = g_tuning.edgeset_slots_per_edge.load();
+      if (spe < 2) spe = 2;
+      if (spe > 16) spe = 16;
+      size_t free_b = 0, total_b = 0;
+      G_TRY(cudaMemGetInfo(&free_b, &total_b));
+      const uint64_t want = g->edgeset_buckets * (uint64_t)spe / 2;
+      const uint64_t rest = (uint64_t)num_edges * 12;  // reverse positions and their join with col, built next
+      if (want * kEdgeSlotsPerBucket * sizeof(uint64_t) + rest < free_b / 2) g->edgeset_buckets = want;
+    }
     G_TRY(cudaMalloc((void**)&g->d_edgeset, g->edgeset_buckets * kEdgeSlotsPerBucket * sizeof(uint64_t)));
     if (int rc = walk_b200_edgeset_build(&csr, g->d_edgeset, g->edgeset_buckets, g->d_flags, s)) return bail(rc);
     G_TRY(cudaMemcpyAsync(&f, g->d_flags, 4, cudaMemcpyDeviceToHost, s));

@@ -80,7 +80,7 @@ class WalkGraph:
 
     def __init__(self, rowptr: torch.Tensor, col: torch.Tensor, *, symmetric: bool = False,
                  use_rowdesc: bool = True, edgeset: bool = False, fused: bool = False, validate: bool = False,
-                 stream=None):
+                 stream=None, edgeset_slots_per_edge: Optional[float] = None):
         if not rowptr.is_cuda:
             raise ValueError("WalkGraph needs CUDA tensors (use HostGraph for host arrays)")
         dev = rowptr.device
@@ -97,6 +97,9 @@ class WalkGraph:
         self.edgeset_buckets = 0
         self.colrev = None
         self.fused = None
+        # size of the edge hash set in 8-byte slots per edge: 2 = half full (the minimum), 4 = a quarter full;
+        # None = the library's tuning (default 4), taken when the table fits half of the free device memory
+        self.edgeset_slots_per_edge = None if edgeset_slots_per_edge is None else max(2.0, float(edgeset_slots_per_edge))
         self.rows_sorted = None   # None: not checked yet (see check_rows_sorted)
         self.n2v_calls = 0        # node2vec calls served: edgeset="auto" builds the hash set on the second
         self._version = (rowptr._version, col._version)
@@ -143,7 +146,17 @@ class WalkGraph:
         if self.edgeset is not None:
             return
         with torch.cuda.device(self.device):
+            # the library's size is the smallest it accepts (half full); a sparser table answers more tests
+            # from their first bucket at the price of its memory
             buckets = _lib.edgeset_buckets(self.num_edges)
+            if self.edgeset_slots_per_edge is not None:
+                buckets = int(buckets * self.edgeset_slots_per_edge / 2.0)
+            else:
+                want = int(buckets * max(2, min(16, _lib.get_tuning("edgeset_slots_per_edge"))) / 2.0)
+                free, _ = torch.cuda.mem_get_info(self.device)
+                cached = torch.cuda.memory_reserved(self.device) - torch.cuda.memory_allocated(self.device)
+                if want * 32 + 12 * self.num_edges < (free + cached) // 2:
+                    buckets = want
             table = torch.empty(buckets * 4, dtype=torch.int64, device=self.device)
             csr = self.csr()
             _lib.check(_lib.lib().walk_b200_edgeset_build(C.byref(csr), table.data_ptr(), buckets,

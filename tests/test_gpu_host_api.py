@@ -21,6 +21,7 @@ def _reset():
     _lib.set_tuning("host_threads", 0)
     _lib.set_tuning("host_single_launch", 1)
     _lib.set_tuning("n2v_pool", 1)
+    _lib.set_tuning("edgeset_slots_per_edge", 4)
     clear_caches()
 
 
@@ -146,9 +147,12 @@ def test_host_entry_reports_bad_input(cuda, golden):
     hg = HostGraph(g["rowptr1"], g["col1"], validate=True)
     assert hg.device_bytes() == (2709 + 10556 + 2708) * 8
     hg.close()
-    hg = HostGraph(g["rowptr1"], g["col1"], edgeset=True)
-    assert hg.device_bytes() == (2709 + 10556 + 2708) * 8 + _lib.edgeset_buckets(10556) * 32 + 10556 * 8
-    hg.close()
+    for slots_per_edge in (2, 4):   # half full (the minimum) and the default, a quarter full
+        _lib.set_tuning("edgeset_slots_per_edge", slots_per_edge)
+        hg = HostGraph(g["rowptr1"], g["col1"], edgeset=True)
+        table = _lib.edgeset_buckets(10556) * slots_per_edge // 2 * 32
+        assert hg.device_bytes() == (2709 + 10556 + 2708) * 8 + table + 10556 * 8
+        hg.close()
 
 
 def test_l2_window_hint_does_not_change_results(cuda, golden):

@@ -139,14 +139,22 @@ def test_malformed_input_is_flagged_not_faulted(cuda, golden):
     rand[3, 2] = 1.0
     start[7] = 2708          # out of range
     start[8] = -5
-    with pytest.raises(RuntimeError, match="status flags"):
-        random_walk(rowptr, col, start, rand, 5, check=True)
-    out = random_walk(rowptr, col, start, rand, 5)
-    torch.cuda.synchronize()
-    assert (out[7] == 2708).all() and (out[8] == -5).all()   # parked on the bad id
-    good = np.ones(2000, dtype=bool)
-    good[[3, 7, 8]] = False
-    np.testing.assert_array_equal(out.cpu().numpy()[good], g["uniform1_n"][good])
+    start[9] = 1 << 40
+    for variant in ("staged16_64regs", "direct"):
+        _lib.set_tuning("uniform_variant", VARIANTS[variant])
+        with pytest.raises(RuntimeError, match="status flags"):
+            random_walk(rowptr, col, start, rand, 5, check=True)
+        out, e = random_walk(rowptr, col, start, rand, 5, return_edges=True)
+        torch.cuda.synchronize()
+        assert (out[7] == 2708).all() and (out[8] == -5).all() and (out[9] == 1 << 40).all()   # parked on the bad id
+        assert (e[[7, 8, 9]] == -1).all()
+        good = np.ones(2000, dtype=bool)
+        good[[3, 7, 8, 9]] = False
+        np.testing.assert_array_equal(out.cpu().numpy()[good], g["uniform1_n"][good])
+        np.testing.assert_array_equal(e.cpu().numpy()[good], g["uniform1_e"][good])
+        from mlx_cluster_b200 import clear_caches
+        clear_caches()   # the cached graph keeps the raised flags
+    _lib.set_tuning("uniform_variant", 0)
     graph = WalkGraph(rowptr, col)
     with pytest.raises(ValueError, match="node id out of range"):
         graph.validate(start)
@@ -186,6 +194,8 @@ def test_every_step_follows_an_edge_at_full_length(cuda):
     for v in ("direct", "staged16"):
         _lib.set_tuning("uniform_variant", VARIANTS[v])
         assert torch.equal(out, random_walk(rowptr, col, start, rand, L))
+        o4, e4 = random_walk(None, None, start, rand, L, graph=fused_graph, return_edges=True, check=True)
+        assert torch.equal(out, o4) and torch.equal(e, e4)
 
 
 def test_draws_generated_in_the_kernel_match_their_host_replay(cuda):
@@ -200,10 +210,13 @@ def test_draws_generated_in_the_kernel_match_their_host_replay(cuda):
         want_n, want_e = oracle.uniform_walk(rowptr, col, start, rand, L, return_edges=True)
         for fused in (False, True):
             g = WalkGraph(torch.from_numpy(rowptr).to(cuda), torch.from_numpy(col).to(cuda), fused=fused)
-            got_n, got_e = random_walk(None, None, torch.from_numpy(start).to(cuda), None, L, graph=g, seed=77,
-                                       return_edges=True, check=True)
-            np.testing.assert_array_equal(got_n.cpu().numpy(), want_n)
-            np.testing.assert_array_equal(got_e.cpu().numpy(), want_e)
+            for variant in (0, 1):
+                _lib.set_tuning("uniform_variant", variant)
+                got_n, got_e = random_walk(None, None, torch.from_numpy(start).to(cuda), None, L, graph=g, seed=77,
+                                           return_edges=True, check=True)
+                np.testing.assert_array_equal(got_n.cpu().numpy(), want_n)
+                np.testing.assert_array_equal(got_e.cpu().numpy(), want_e)
+            _lib.set_tuning("uniform_variant", 0)
         for world in (2, 3):
             for r in range(world):
                 part = random_walk(None, None, torch.from_numpy(start[r::world].copy()).to(cuda), None, L, graph=g,
