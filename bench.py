@@ -48,6 +48,8 @@ RMAT = dict(a=0.57, b=0.19, c=0.19, d=0.05)
 # which does not depend on the graph's size: every access misses to DRAM in both cases) times the random
 # accesses one launch of this run issues, counted in this run.
 NCU_SMALL_CASE = {
+    "node2vec_tri": dict(workload="node2vec_rmat20", dram_bytes=19.60e9 * 0.6, accesses=346134263 * 0.6,
+                         source="profiles/node2vec_pool_tri_kernel__node2vec_rmat20.md"),
     "node2vec": dict(workload="node2vec_rmat20", dram_bytes=19.60e9, accesses=346134263,
                      source="profiles/node2vec_pool_kernel__node2vec_rmat20.md"),
     "uniform": dict(workload="uniform_rmat20", dram_bytes=4.70e9, accesses=53816512,
@@ -394,7 +396,9 @@ def run_workload(args, name, wl, dev, world, rank, barrier, allmax, allsum, ligh
     t_prep = time.perf_counter()
     graph = WalkGraph(rowptr, col, symmetric=True, edgeset=(wl["kind"] == "node2vec" and args.membership == "hash"),
                       fused=(wl["kind"] == "uniform" and not args.no_fused),
-                      edgeset_slots_per_edge=args.edgeset_slots_per_edge)
+                      edgeset_slots_per_edge=args.edgeset_slots_per_edge,
+                      trifilter=(wl["kind"] == "node2vec" and args.membership == "hash" and not args.no_trifilter),
+                      trifilter_max_row=args.trifilter_max_row)
     torch.cuda.synchronize(dev)
     prep_s = time.perf_counter() - t_prep
 
@@ -407,7 +411,10 @@ def run_workload(args, name, wl, dev, world, rank, barrier, allmax, allsum, ligh
         free_b = torch.cuda.mem_get_info(dev)[0]
         need_rest = rows * row_bytes * 2  # every rank's own block, plus slack
         budget = int(min(max(free_b - need_rest, 0) * 0.8, args.gather_window_gb * 1e9))
-        window_rows = int(min(n_walks, budget // row_bytes))
+        # the window is rank 0's to hold, and every rank must cut the same windows: rank 0's figure goes to all
+        agreed = torch.tensor([int(min(n_walks, budget // row_bytes))], dtype=torch.int64, device=dev)
+        dist.broadcast(agreed, 0)
+        window_rows = int(agreed.item())
         if window_rows >= min(n_walks, 1 << 16):
             whole = window_rows >= n_walks
             gather_plan = {"window_rows": window_rows, "whole": whole}
@@ -435,6 +442,18 @@ def run_workload(args, name, wl, dev, world, rank, barrier, allmax, allsum, ligh
         gathered_bytes = 8 * cnt["loads"] + 8 * rows * (L + 1) + 8 * rows
         sampled_steps = cnt["steps_sampled"] + cnt["steps_deg1"] + cnt["steps_first"]
         rand = None
+        cnt_kernel = None
+        if graph.colrev16 is not None:
+            # the triangle-filter kernel reads less than the algorithm's counts say: count what it reads itself
+            _lib.set_tuning("n2v_count_kernel", 1)
+            _, cnt_kernel = rejection_sampling(None, None, start, L, wl["p"], wl["q"], graph=graph, seed=PHILOX_SEED,
+                                               walk_index_base=b, walk_index_stride=stride, out=out,
+                                               return_counters=True, check=True)
+            _lib.set_tuning("n2v_count_kernel", 0)
+            if _lib.last_kernel() != "node2vec_pool_tri_kernel":
+                cnt_kernel = None
+            else:
+                gathered_bytes = 8 * cnt_kernel["loads"] + 8 * rows * (L + 1)
 
         def step():
             rejection_sampling(None, None, start, L, wl["p"], wl["q"], graph=graph, seed=PHILOX_SEED,
@@ -444,6 +463,7 @@ def run_workload(args, name, wl, dev, world, rank, barrier, allmax, allsum, ligh
         rand = torch.rand((rows, L), generator=gen, device=dev)
         deg = rowptr.diff()
         cnt = {}
+        cnt_kernel = None
         random_walk(None, None, start, rand, L, graph=graph, out=out, check=True)
         moved = 0
         for c0 in range(0, rows, 1 << 22):  # in slices: the index tensor of the whole matrix would not fit beside it
@@ -474,18 +494,21 @@ def run_workload(args, name, wl, dev, world, rank, barrier, allmax, allsum, ligh
     peak, peak_kind = measured_peak_gbs()
     achieved = allsum(alg_bytes / (kernel_ms * 1e-3) / 1e9) / world  # mean per-GPU GB/s
     # random accesses one launch issues: every gather is one; a hash bucket (counted as four 8-byte loads) is one too
-    if wl["kind"] == "node2vec":
+    if wl["kind"] == "node2vec" and cnt_kernel is not None:
+        accesses = cnt_kernel["loads"] - 3 * cnt_kernel["probes"] - cnt_kernel["gathers16"]
+    elif wl["kind"] == "node2vec":
         accesses = cnt["loads"] - (3 * cnt["probes"] if args.membership == "hash" else 0)
     else:
         accesses = (moved + 2 * rows) if not args.no_fused else (2 * moved + rows)
-    small = NCU_SMALL_CASE[wl["kind"]]
+    small = NCU_SMALL_CASE["node2vec_tri" if cnt_kernel is not None else wl["kind"]]
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                 "peak_source": f"of {peak_kind}",
                 "traffic": small["dram_bytes"] / small["accesses"] * allsum(float(accesses)) / world,
                 "traffic_source": f"{small['dram_bytes'] / small['accesses']:.1f} DRAM bytes per random access (ncu on "
                                   f"{small['workload']}, {small['source']}) x the random accesses one launch of this run "
                                   "issues per GPU, counted in this run",
-                "kernel": "node2vec_pool_kernel (node2vec_walk_kernel where the pooled form does not apply)" if
+                "kernel": ("node2vec_pool_tri_kernel" if cnt_kernel is not None else
+                           "node2vec_pool_kernel (node2vec_walk_kernel where the pooled form does not apply)") if
                 wl["kind"] == "node2vec" else "uniform_walk_staged_kernel", "kernel_ms": kernel_ms,
                 "kernel_launched": _lib.last_kernel(), "random_accesses_per_launch": int(accesses),
                 "algorithmic_bytes_per_launch": alg_bytes, "gathered_bytes_per_launch": gathered_bytes,
@@ -493,6 +516,8 @@ def run_workload(args, name, wl, dev, world, rank, barrier, allmax, allsum, ligh
                 "algorithmic_bytes_per_walk_step": alg_bytes / max(1, rows * L)}
     if cnt:
         roofline["counters"] = cnt
+    if cnt_kernel is not None:
+        roofline["kernel_counters"] = {k: cnt_kernel[k] for k in ("loads", "attempts", "membership", "probes", "gathers16", "filtered")}
     # second ceiling: the device's rate of dependent random gathers that miss L2 (measured now)
     if rank == 0 and not args.no_probe:
         ceiling = _lib.gather_probe(2 << 30, 32)
@@ -500,6 +525,18 @@ def run_workload(args, name, wl, dev, world, rank, barrier, allmax, allsum, ligh
                                      "achieved_gathers_per_s": accesses / (kernel_ms * 1e-3),
                                      "frac": accesses / (kernel_ms * 1e-3) / ceiling,
                                      "note": "gathers issued, an upper bound on DRAM-missing ones"}
+
+    # ---- the same launches without the triangle filter (a structure that takes seconds to build per graph)
+    plain = None
+    if cnt_kernel is not None and not light:
+        _lib.set_tuning("n2v_tri", 0)
+        p_ms, p_per, _ = time_launches(step, min(steps, 10), args.warmup, stream, None, barrier)
+        _lib.set_tuning("n2v_tri", 1)
+        p_ms = allmax(p_ms / min(steps, 10))
+        plain = {"ms_per_step": p_ms, "value": walks_timed * L / (p_ms * 1e-3), "unit": "steps/s",
+                 "kernel": "node2vec_pool_kernel", "steps": min(steps, 10),
+                 "roofline_frac": allsum(alg_bytes / (statistics.mean(p_per) * 1e-3) / 1e9) / world / peak}
+        step()  # leave the filtered kernel's matrix in `out` for the checks below
 
     # ---- parity of what was just timed: the first rows of the matrix against the CPU restatement (untimed)
     parity = {}
@@ -576,7 +613,8 @@ def run_workload(args, name, wl, dev, world, rank, barrier, allmax, allsum, ligh
         t_up = time.perf_counter()
         hg = HostGraph(h_rowptr, h_col, symmetric=True, device=dev,
                        edgeset=(wl["kind"] == "node2vec" and args.membership == "hash"),
-                       fused=(wl["kind"] == "uniform" and not args.no_fused))
+                       fused=(wl["kind"] == "uniform" and not args.no_fused),
+                       trifilter=(wl["kind"] == "node2vec" and args.membership == "hash" and not args.no_trifilter))
         upload_s = time.perf_counter() - t_up
 
         def host_step():
@@ -654,6 +692,8 @@ def run_workload(args, name, wl, dev, world, rank, barrier, allmax, allsum, ligh
         "graph_prepare_s_once": prep_s,
     }
     line.update(parity)
+    if plain is not None:
+        line["without_trifilter"] = plain
     if gather is not None:
         line["gather"] = gather
     return line
@@ -672,7 +712,9 @@ def run_ours(args, wl):
         # NCCL writes its log lines (the version banner included) to stdout unless told otherwise; stdout is for
         # the JSON line. The log level itself is the caller's business and is left alone.
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-        dist.init_process_group("nccl", device_id=dev)
+        # a collective that does not complete within minutes is a bug of this script, not a slow step
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=args.collective_timeout_s))
     barrier = (lambda: dist.barrier()) if world > 1 else None
 
     def allmax(x):
@@ -733,6 +775,11 @@ def main():
     ap.add_argument("--edgeset-slots-per-edge", type=float, default=None,
                     help="node2vec: size of the edge hash set (2 = half full, the library's minimum; 4 = a quarter full; "
                          "default: the library's tuning, 4 when it fits)")
+    ap.add_argument("--no-trifilter", action="store_true",
+                    help="node2vec: do not build the triangle filter (seconds per graph; the walks then run the plain pooled kernel)")
+    ap.add_argument("--trifilter-max-row", type=int, default=None,
+                    help="node2vec triangle filter: leave edges whose shorter row is longer than this unfiltered "
+                         "(0: none; default: the library's tuning, 1024)")
     ap.add_argument("--no-probe", action="store_true", help="skip the random-gather ceiling probe")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -745,6 +792,7 @@ def main():
     ap.add_argument("--gather-windows", type=int, default=4,
                     help="N > 1, matrix larger than the window: how many windows to gather and time (0 = all)")
     ap.add_argument("--no-ceiling", action="store_true", help="skip the host-side ceiling probes of the e2e leg")
+    ap.add_argument("--collective-timeout-s", type=int, default=150, help="N > 1: process-group timeout")
     ap.add_argument("--tune", action="append", default=[], help="key=value passed to walk_b200_set_tuning")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)

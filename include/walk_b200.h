@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define WALK_B200_ABI_VERSION 8
+#define WALK_B200_ABI_VERSION 9
 
 /* ---- return codes ---- */
 #define WALK_B200_OK 0
@@ -61,6 +61,9 @@ extern "C" {
 
 #define WALK_B200_CSR_WANT_FUSED 0x4u /* walk_b200_graph_create only: also build the fused edge records */
 
+#define WALK_B200_CSR_WANT_TRIFILTER 0x8u /* walk_b200_graph_create only, with _SYMMETRIC and _WANT_EDGESET: also build the
+                                             triangle filter (walk_b200_trifilter_build; tuning trifilter_max_row) */
+
 typedef struct walk_b200_csr {
   const int64_t* rowptr;   /* device, [num_nodes + 1] */
   const int64_t* col;      /* device, [num_edges]; node2vec needs each row sorted ascending */
@@ -78,6 +81,8 @@ typedef struct walk_b200_csr {
                               walk then makes one gather per step; needs rowdesc */
   const uint64_t* colrev;  /* device, [num_edges], from walk_b200_colrev_build, or NULL; only used together with
                               edgeset and rowdesc */
+  const void* colrev16;    /* device, [num_edges] 16-byte records from walk_b200_trifilter_build, or NULL; only used
+                              together with colrev, edgeset and rowdesc on a graph flagged WALK_B200_CSR_SYMMETRIC */
 } walk_b200_csr;
 
 /* node2vec instrumentation slots (device uint64[WALK_B200_COUNTER_COUNT], caller zeroes them) */
@@ -92,6 +97,8 @@ enum {
   WALK_B200_CNT_STEPS_FIRST,
   WALK_B200_CNT_FORMULA_PROBES, /* sum over membership tests of ceil(log2(deg(candidate) + 1)): what a binary search
                                    of the candidate's row, the reference's is_neighbor(x, t) done in log time, would probe */
+  WALK_B200_CNT_GATHERS16,      /* triangle-filter kernel only: 16-byte candidate gathers (each also counted as 2 loads) */
+  WALK_B200_CNT_FILTERED,       /* triangle-filter kernel only: attempts the filter rejected without a gather */
   WALK_B200_COUNTER_COUNT
 };
 
@@ -204,6 +211,21 @@ int walk_b200_revpos_build(const walk_b200_csr* g, uint32_t* revpos, uint32_t* s
  * needs no separate look-up of the reverse position. revpos itself may be freed afterwards.
  */
 int walk_b200_colrev_build(const walk_b200_csr* g, uint64_t* colrev, uint32_t* status_flags, void* stream);
+
+/*
+ * Triangle filter for node2vec on an undirected graph: colrev16[e] = {colrev[e], filter word of e} (caller scratch
+ * of 16 * num_edges bytes, 16-byte aligned; g needs colrev, edgeset and WALK_B200_CSR_SYMMETRIC). The membership
+ * test "is the previous node t a neighbour of the candidate x" (is_neighbor, random_walks/BiasedRandomWalk.cpp:20-28,
+ * called at :88) can only say yes when x is a common neighbour of t and the node v the walk stands on. Bit k of the
+ * word of edge (t -> v) is set iff such a common neighbour sits at a position p of v's row with p mod 64 == k, so a
+ * walk that arrived by that edge knows from the position it drew alone, before gathering the candidate, that an
+ * attempt which only the membership rule could accept fails. With it a launch at p=0.25, q=4 gathers about half as
+ * much. Building it costs one edge-set look-up per entry of the shorter row of every undirected edge (seconds on a
+ * graph of 5e8 edges; worth it for a graph that is walked many times); edges whose shorter row exceeds max_row
+ * (0 = no limit) keep an all-ones word, i.e. go unfiltered. Results are identical with and without it.
+ */
+int walk_b200_trifilter_build(const walk_b200_csr* g, void* colrev16, int64_t max_row, uint32_t* status_flags,
+                              void* stream);
 
 /*
  * Full check the reference never makes (it reinterprets whatever it is given,
@@ -395,7 +417,7 @@ int walk_b200_gather_probe_ex(size_t array_bytes, int32_t iters, int32_t chains,
 /* Kernel variant and transport selection; unknown keys fail. None of them changes a result (but see n2v_max_attempts).
  *   uniform_variant, uniform_fused, l2_hints, l2_fetch_granularity, use_rowdesc
  *   n2v_idx, n2v_member, n2v_rev, n2v_pool (0 per-lane kernel, 1 pooled kernel where it wins, 2 always),
- *   n2v_batch_lanes, n2v_batch_trips, n2v_draw_loop, n2v_blocks_per_sm,
+ *   n2v_batch_lanes, n2v_batch_trips, n2v_draw_loop, n2v_blocks_per_sm, n2v_tri (0: ignore a graph's triangle filter),
  *   edgeset_slots_per_edge (size of the edge hash set a resident graph builds for itself, in 8-byte slots per
  *   edge: 2 = half full, the minimum; default 4, taken when the table fits half of the free device memory),
  *   n2v_max_attempts (rejections after which a step gives up, at most WALK_B200_MAX_ATTEMPTS: the one key that

@@ -15,16 +15,16 @@ OK = 0
 ERR_INVALID_ARG, ERR_BAD_PQ, ERR_CUDA, ERR_CSR_INVALID, ERR_UNSUPPORTED, ERR_DEVICE_FLAGS = 1, 2, 3, 4, 5, 6
 FLAG_BAD_NODE, FLAG_BAD_EDGE, FLAG_ATTEMPT_CAP, FLAG_BAD_ROWPTR = 0x1, 0x2, 0x4, 0x8
 FLAG_DESC_OVERFLOW, FLAG_UNSORTED_ROW, FLAG_EDGESET_FULL = 0x10, 0x20, 0x80
-CSR_SYMMETRIC, CSR_WANT_EDGESET, CSR_WANT_FUSED = 0x1, 0x2, 0x4
+CSR_SYMMETRIC, CSR_WANT_EDGESET, CSR_WANT_FUSED, CSR_WANT_TRIFILTER = 0x1, 0x2, 0x4, 0x8
 COUNTER_NAMES = ("loads", "attempts", "membership", "probes",
-                 "steps_deg0", "steps_deg1", "steps_sampled", "steps_first", "formula_probes")
+                 "steps_deg0", "steps_deg1", "steps_sampled", "steps_first", "formula_probes", "gathers16", "filtered")
 
 # every symbol include/walk_b200.h declares
 EXPORTS = (
     "walk_b200_abi_version", "walk_b200_last_error", "walk_b200_launch_count", "walk_b200_last_kernel",
     "walk_b200_uniform_walk", "walk_b200_uniform_walk_philox", "walk_b200_uniform_draw",
     "walk_b200_uniform_draws", "walk_b200_node2vec_walk", "walk_b200_rowdesc_pack",
-    "walk_b200_csr_validate", "walk_b200_edgeset_buckets", "walk_b200_edgeset_build", "walk_b200_revpos_build", "walk_b200_colrev_build", "walk_b200_fused_build", "walk_b200_philox4x32_10", "walk_b200_node2vec_draw",
+    "walk_b200_csr_validate", "walk_b200_edgeset_buckets", "walk_b200_edgeset_build", "walk_b200_revpos_build", "walk_b200_colrev_build", "walk_b200_trifilter_build", "walk_b200_fused_build", "walk_b200_philox4x32_10", "walk_b200_node2vec_draw",
     "walk_b200_node2vec_thresholds", "walk_b200_shard_range", "walk_b200_shard_count_cyclic",
     "walk_b200_graph_create", "walk_b200_graph_destroy", "walk_b200_graph_csr",
     "walk_b200_graph_device_bytes", "walk_b200_uniform_walk_host", "walk_b200_node2vec_walk_host",
@@ -43,7 +43,7 @@ class Csr(C.Structure):
     _fields_ = [("rowptr", C.c_void_p), ("col", C.c_void_p), ("num_nodes", C.c_int64),
                 ("num_edges", C.c_int64), ("rowdesc", C.c_void_p), ("flags", C.c_uint32),
                 ("reserved", C.c_uint32), ("edgeset", C.c_void_p), ("edgeset_buckets", C.c_uint64),
-                ("revpos", C.c_void_p), ("fused", C.c_void_p), ("colrev", C.c_void_p)]
+                ("revpos", C.c_void_p), ("fused", C.c_void_p), ("colrev", C.c_void_p), ("colrev16", C.c_void_p)]
 
 
 class WalkError(RuntimeError):
@@ -82,6 +82,7 @@ def lib():
     L.walk_b200_edgeset_build.argtypes = [C.POINTER(Csr), vp, u64, vp, vp]
     L.walk_b200_revpos_build.argtypes = [C.POINTER(Csr), vp, vp, vp]
     L.walk_b200_colrev_build.argtypes = [C.POINTER(Csr), vp, vp, vp]
+    L.walk_b200_trifilter_build.argtypes = [C.POINTER(Csr), vp, i64, vp, vp]
     L.walk_b200_fused_build.argtypes = [C.POINTER(Csr), vp, vp, vp]
     L.walk_b200_philox4x32_10.argtypes = [vp, vp, vp]
     L.walk_b200_philox4x32_10.restype = None

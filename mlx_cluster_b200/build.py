@@ -14,7 +14,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libwalk_b200.so"
 SOURCES = [CSRC / "walk_b200.cu", CSRC / "csr_build.cu", CSRC / "host_widen.cpp"]
-HEADERS = [CSRC / "walk_kernels.cuh", CSRC / "philox.cuh", CSRC / "host_widen.h", CSRC / "n2v_pool.cuh", CSRC / "host_common.h", PKG.parent / "include" / "walk_b200.h"]
+HEADERS = [CSRC / "walk_kernels.cuh", CSRC / "philox.cuh", CSRC / "host_widen.h", CSRC / "n2v_pool.cuh", CSRC / "n2v_pool_tri.cuh", CSRC / "host_common.h", PKG.parent / "include" / "walk_b200.h"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -572,6 +572,91 @@ __global__ void __launch_bounds__(kBlock) revpos_build_kernel(const int64_t* __r
 }
 
 // ---------------------------------------------------------------------------------
+// triangle filter: per directed edge, which positions of the target's row hold common neighbours
+// ---------------------------------------------------------------------------------
+// colrev16[e] = {colrev[e], filter(e)}. For e = (a -> b), bit k of filter(e) is set iff some w in N(a) & N(b)
+// sits at a position p of b's row with p mod 64 == k: a walk that came from a and stands on b need not look at
+// a candidate drawn at a position whose bit is clear to know that it is not a neighbour of a.
+// Work is done once per undirected edge, from the end with the shorter row (ties: the smaller id): one warp
+// walks that row, asks the edge hash set for each entry whether it is a neighbour of the other end, and for
+// the hits sets the bit of the entry's position in its own row (filter of the edge back) and, after a binary
+// search, of its position in the other end's row (filter of the edge itself). An edge whose shorter row
+// exceeds max_row, a self-loop and an edge without a reverse keep the all-ones word the host wrote before the
+// launch: no filtering. Warps take chunks of 64 edges from a counter.
+__device__ __forceinline__ bool edge_lookup(const uint64_t* __restrict__ table, uint64_t num_buckets, uint64_t key) {
+  uint64_t b = edge_bucket(key, num_buckets);
+  for (int probe = 0; probe < kEdgeMaxProbe; probe++) {
+    const ulonglong2 h0 = ld16(table + b * kEdgeSlotsPerBucket, 0), h1 = ld16(table + b * kEdgeSlotsPerBucket + 2, 0);
+    if (h0.x == key || h0.y == key || h1.x == key || h1.y == key) return true;
+    if (h0.x == kEdgeEmpty || h0.y == kEdgeEmpty || h1.x == kEdgeEmpty || h1.y == kEdgeEmpty) return false;
+    if (++b == num_buckets) b = 0;
+  }
+  return true;  // a chain that long does not occur in a table at most half full; "maybe" is the safe answer
+}
+
+__global__ void __launch_bounds__(kBlock) trifilter_build_kernel(const int64_t* __restrict__ rowptr,
+                                                                 const int64_t* __restrict__ col,
+                                                                 const uint64_t* __restrict__ colrev,
+                                                                 const uint64_t* __restrict__ edgeset, uint64_t edgeset_buckets,
+                                                                 int64_t num_nodes, int64_t num_edges, int64_t max_row,
+                                                                 ulonglong2* __restrict__ colrev16,
+                                                                 unsigned long long* queue) {
+  constexpr unsigned kFull = 0xffffffffu;
+  constexpr int64_t kChunk = 64;
+  const int lane = threadIdx.x & 31;
+  while (true) {
+    unsigned long long chunk = 0;
+    if (lane == 0) chunk = atomicAdd(queue, 1ull);
+    chunk = __shfl_sync(kFull, chunk, 0);
+    const int64_t e0 = (int64_t)chunk * kChunk;
+    if (e0 >= num_edges) break;
+    const int64_t e1 = min(e0 + kChunk, num_edges);
+    // source row of e0: last a with rowptr[a] <= e0; later edges of the chunk move on from there
+    int64_t lo = 0, hi = num_nodes;
+    while (hi - lo > 1) {
+      const int64_t mid = lo + (hi - lo) / 2;
+      if (__ldg(rowptr + mid) <= e0) lo = mid; else hi = mid;
+    }
+    int64_t a = lo;
+    int64_t a_end = __ldg(rowptr + a + 1);
+    for (int64_t e = e0; e < e1; e++) {
+      while (e >= a_end) { a++; a_end = __ldg(rowptr + a + 1); }
+      const uint64_t cr = colrev[e];
+      if (lane == 0) colrev16[e].x = cr;
+      const int64_t b = (int64_t)(cr & 0xffffffffull);
+      const uint32_t rev = (uint32_t)(cr >> 32);
+      if (rev >= 0xfffffffeu || b == a || (uint64_t)b >= (uint64_t)num_nodes) continue;  // no edge back, or a self-loop
+      const int64_t a_rs = __ldg(rowptr + a), b_rs = __ldg(rowptr + b);
+      const int64_t da = a_end - a_rs, db = __ldg(rowptr + b + 1) - b_rs;
+      if (!(da < db || (da == db && a < b))) continue;  // done from the other end
+      if (max_row > 0 && da > max_row) continue;
+      unsigned long long here = 0, there = 0;  // bits of positions in a's row / in b's row
+      for (int64_t i = lane; i < da; i += 32) {
+        const int64_t w = __ldg(col + a_rs + i);
+        if (!edge_lookup(edgeset, edgeset_buckets, edge_key((uint64_t)b, (uint64_t)w))) continue;
+        here |= 1ull << (i & 63);
+        int64_t p = b_rs, q = b_rs + db;  // position of w in b's row (it is there: the set just said so)
+        while (p < q) {
+          const int64_t mid = p + (q - p) / 2;
+          const int64_t c = __ldg(col + mid);
+          if (c == w) { there |= 1ull << ((mid - b_rs) & 63); break; }
+          if (c < w) p = mid + 1; else q = mid;
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        here |= __shfl_xor_sync(kFull, here, o);
+        there |= __shfl_xor_sync(kFull, there, o);
+      }
+      if (lane == 0) {
+        colrev16[e].y = there;    // standing on b, came from a: candidates are positions of b's row
+        colrev16[rev].y = here;   // standing on a, came from b
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
 // node2vec walk
 // ---------------------------------------------------------------------------------
 struct Node2vecParams {
@@ -581,6 +666,7 @@ struct Node2vecParams {
   const uint64_t* edgeset;
   uint64_t edgeset_buckets;
   const uint64_t* colrev;  // REV kernels: col[e] | revpos[e] << 32
+  const ulonglong2* colrev16;  // triangle-filter kernel: {colrev[e], filter word of e}
   int64_t num_nodes, num_edges;
   const int64_t* start;
   int64_t num_walks;

@@ -34,7 +34,7 @@ def test_status_codes_and_flags_match_header():
     assert defs["WALK_B200_CSR_SYMMETRIC"] == _lib.CSR_SYMMETRIC
     n_counters = len(re.findall(r"^\s+WALK_B200_CNT_[A-Z0-9_]+", header, flags=re.M))
     assert n_counters == len(_lib.COUNTER_NAMES)
-    assert C.sizeof(_lib.Csr) == 88
+    assert C.sizeof(_lib.Csr) == 96
     assert defs["WALK_B200_CSR_WANT_FUSED"] == _lib.CSR_WANT_FUSED
     assert defs["WALK_B200_FLAG_EDGESET_FULL"] == _lib.FLAG_EDGESET_FULL
     assert defs["WALK_B200_CSR_WANT_EDGESET"] == _lib.CSR_WANT_EDGESET

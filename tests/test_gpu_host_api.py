@@ -110,6 +110,28 @@ def test_narrow_transport_is_invisible(cuda):
             np.testing.assert_array_equal(e.numpy(), want_be)
 
 
+def test_resident_graph_with_triangle_filter(cuda, golden):
+    """The host entry's single launch with the triangle filter (both transports) against the restatement."""
+    g = golden
+    start = np.concatenate([g["start2"], g["start2"][::-1]]).astype(np.int64)
+    want, want_e = oracle.node2vec_walk(g["rowptr2"], g["col2"], start, 20, 0.25, 4.0, seed=21, return_edges=True)
+    hg = HostGraph(g["rowptr2"], g["col2"], symmetric=True, edgeset=True, trifilter=True)
+    assert hg.device_bytes() > (2709 + 2 * 10556 + 2708) * 8 + 10556 * 16
+    lib = _lib.lib()
+    for narrow in (1, 0):
+        _lib.set_tuning("host_narrow", narrow)
+        for with_edges in (False, True):
+            out = np.full((start.size, 21), -3, dtype=np.int64)
+            e_out = np.full((start.size, 20), -3, dtype=np.int64)
+            _lib.check(lib.walk_b200_node2vec_walk_host(hg._h, start.ctypes.data, start.size, 20, 0.25, 4.0, 21, 0, 1,
+                                                        out.ctypes.data, e_out.ctypes.data if with_edges else None))
+            assert _lib.last_kernel() == "node2vec_pool_tri_kernel"
+            np.testing.assert_array_equal(out, want)
+            if with_edges:
+                np.testing.assert_array_equal(e_out, want_e)
+    hg.close()
+
+
 def test_transport_choice_is_reported(cuda, golden):
     g = golden
     _lib.set_tuning("host_narrow", 2)

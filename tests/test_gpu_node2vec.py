@@ -25,6 +25,7 @@ def _reset_tuning():
     _lib.set_tuning("n2v_pool", 1)
     _lib.set_tuning("l2_hints", 3)
     _lib.set_tuning("n2v_max_attempts", 1 << 22)
+    _lib.set_tuning("n2v_tri", 1)
 
 
 def run_gpu(dev, rowptr, col, start, L, p, q, *, seed=0, base=0, symmetric=False, rowdesc=True,
@@ -327,3 +328,94 @@ def test_properties_at_scale(cuda):
     sub = torch.stack([rejection_sampling(rowptr, col, rows[i:i + 1], L, 0.25, 4.0, seed=3, symmetric=True,
                                           walk_index_base=i)[0] for i in range(0, 64)])
     np.testing.assert_array_equal(sub.cpu().numpy(), n_o[:64])
+
+
+def _filter_words_by_definition(rowptr, col):
+    """Bit k of the word of edge e = (a -> b): some common neighbour of a and b sits at a position p of b's row
+    with p % 64 == k. Plain numpy, small graphs only."""
+    n = rowptr.size - 1
+    rows = [col[rowptr[v]:rowptr[v + 1]] for v in range(n)]
+    src = np.repeat(np.arange(n), np.diff(rowptr))
+    words = np.zeros(col.size, dtype=np.uint64)
+    for e in range(col.size):
+        a, b = int(src[e]), int(col[e])
+        if a == b:
+            words[e] = np.uint64(0xffffffffffffffff)   # self-loops go unfiltered
+            continue
+        common = np.intersect1d(rows[a], rows[b], assume_unique=True)
+        pos = np.searchsorted(rows[b], common)
+        w = 0
+        for p in pos:
+            w |= 1 << (int(p) & 63)
+        words[e] = np.uint64(w)
+    return words
+
+
+def test_triangle_filter_words_and_walks(cuda, golden):
+    """The filter words equal their definition, and walks that use them are the restatement's walks."""
+    g = golden
+    rng = np.random.default_rng(31)
+    graphs_small = [(g["rowptr2"], g["col2"]), random_csr(rng, 300, 9.0, frac_isolated=0.1, symmetric=True),
+                    random_csr(rng, 200, 160.0, frac_isolated=0.0, symmetric=True)]   # the last one: rows longer than 64
+    for rowptr, col in graphs_small:
+        graph = WalkGraph(torch.from_numpy(rowptr).to(cuda), torch.from_numpy(col).to(cuda), symmetric=True,
+                          edgeset=True, trifilter=True)
+        rec = graph.colrev16.cpu().numpy()
+        np.testing.assert_array_equal(rec[:, 0], graph.colrev.cpu().numpy())
+        np.testing.assert_array_equal(rec[:, 1].view(np.uint64), _filter_words_by_definition(rowptr, col))
+        n_nodes = rowptr.size - 1
+        start = np.concatenate([np.arange(n_nodes), rng.integers(0, n_nodes, 3000)]).astype(np.int64)
+        st = torch.from_numpy(start).to(cuda)
+        for pq in PQS:
+            n_o, e_o = oracle.node2vec_walk(rowptr, col, start, 30, *pq, seed=17, return_edges=True)
+            _lib.set_tuning("n2v_pool", 2)
+            for edges in (True, False):
+                res = rejection_sampling(None, None, st, 30, *pq, graph=graph, seed=17, return_edges=edges, check=True)
+                assert _lib.last_kernel() == "node2vec_pool_tri_kernel"
+                np.testing.assert_array_equal((res[0] if edges else res).cpu().numpy(), n_o)
+                if edges:
+                    np.testing.assert_array_equal(res[1].cpu().numpy(), e_o)
+            _lib.set_tuning("n2v_tri", 0)
+            rejection_sampling(None, None, st, 30, *pq, graph=graph, seed=17)
+            assert _lib.last_kernel() == "node2vec_pool_kernel"
+            _lib.set_tuning("n2v_tri", 1)
+        # the attempt cap runs out in the filtered kernel as in the others
+        _lib.set_tuning("n2v_max_attempts", 3)
+        n_o, e_o = oracle.node2vec_walk(rowptr, col, start, 30, 0.25, 4.0, seed=17, return_edges=True, max_attempts=3)
+        n, e = rejection_sampling(None, None, st, 30, 0.25, 4.0, graph=graph, seed=17, return_edges=True)
+        np.testing.assert_array_equal(n.cpu().numpy(), n_o)
+        np.testing.assert_array_equal(e.cpu().numpy(), e_o)
+        from mlx_cluster_b200 import read_status
+        assert read_status(graph) == _lib.FLAG_ATTEMPT_CAP
+        _lib.set_tuning("n2v_max_attempts", 1 << 22)
+    # a limit on the row length leaves long rows unfiltered (all ones), never wrong
+    rowptr, col = graphs_small[2]
+    capped = WalkGraph(torch.from_numpy(rowptr).to(cuda), torch.from_numpy(col).to(cuda), symmetric=True, edgeset=True,
+                       trifilter=True, trifilter_max_row=30)
+    words = capped.colrev16.cpu().numpy()[:, 1].view(np.uint64)
+    want = _filter_words_by_definition(rowptr, col)
+    assert ((words == want) | (words == np.uint64(0xffffffffffffffff))).all() and (words != want).any()
+    with pytest.raises(ValueError, match="undirected"):
+        WalkGraph(torch.from_numpy(rowptr).to(cuda), torch.from_numpy(col).to(cuda), edgeset=True, trifilter=True)
+
+
+def test_triangle_filter_at_scale(cuda):
+    """Graph larger than L2: the filtered kernel reproduces the unfiltered matrix and every 997th row of the restatement."""
+    rowptr, col = graphs.rmat_csr(20, 16, seed=2, device=cuda)
+    n_nodes = rowptr.numel() - 1
+    start = torch.arange(n_nodes, dtype=torch.int64, device=cuda)
+    L = 40
+    graph = WalkGraph(rowptr, col, symmetric=True, edgeset=True, trifilter=True)
+    _lib.set_tuning("n2v_tri", 0)
+    plain = rejection_sampling(None, None, start, L, 0.25, 4.0, graph=graph, seed=3, check=True)
+    assert _lib.last_kernel() == "node2vec_pool_kernel"
+    _lib.set_tuning("n2v_tri", 1)
+    for pq in ((0.25, 4.0), (0.5, 2.0)):
+        got = rejection_sampling(None, None, start, L, *pq, graph=graph, seed=3, check=True)
+        assert _lib.last_kernel() == "node2vec_pool_tri_kernel"
+        if pq == (0.25, 4.0):
+            assert torch.equal(got, plain)
+        picked = torch.arange(0, n_nodes, 997, device=cuda)
+        want = oracle.node2vec_walk(rowptr.cpu().numpy(), col.cpu().numpy(), picked.cpu().numpy(), L, *pq, seed=3,
+                                    walk_index_stride=997)
+        np.testing.assert_array_equal(got[picked].cpu().numpy(), want)
