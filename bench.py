@@ -48,7 +48,7 @@ RMAT = dict(a=0.57, b=0.19, c=0.19, d=0.05)
 # which does not depend on the graph's size: every access misses to DRAM in both cases) times the random
 # accesses one launch of this run issues, counted in this run.
 NCU_SMALL_CASE = {
-    "node2vec_tri": dict(workload="node2vec_rmat20", dram_bytes=19.60e9 * 0.6, accesses=346134263 * 0.6,
+    "node2vec_tri": dict(workload="node2vec_rmat20", dram_bytes=11.11e9, accesses=208205614,
                          source="profiles/node2vec_pool_tri_kernel__node2vec_rmat20.md"),
     "node2vec": dict(workload="node2vec_rmat20", dram_bytes=19.60e9, accesses=346134263,
                      source="profiles/node2vec_pool_kernel__node2vec_rmat20.md"),
