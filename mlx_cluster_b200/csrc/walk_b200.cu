@@ -335,24 +335,29 @@ bool rev_pays(const Node2vecParams& P) {
 // steps are long (many rejected attempts per step, i.e. where the reverse positions pay: 123 vs
 // 164 ms at (p, q) = (0.25, 4) on R-MAT 24) and loses where almost every first candidate is accepted
 // and a step is three short trips (8.9 vs 7.9 ms at (1, 2) on R-MAT 22): 1 = where it wins, 2 = always.
-bool pool_applies(const Node2vecParams& P, int member) {
-  const int mode = g_tuning.n2v_pool.load();
-  return mode != 0 && (mode == 2 || rev_pays(P)) && member == MEMBER_HASH && P.colrev && P.desc && !P.counters &&
+bool pool_possible(const Node2vecParams& P, int member) {  // what the pooled kernels are built for
+  return g_tuning.n2v_pool.load() != 0 && member == MEMBER_HASH && P.colrev && P.desc && !P.counters &&
          P.num_nodes <= 0x7fffffffll && P.num_edges < 0xfffffffell && P.edgeset_buckets < 0xffffffffull &&
          P.num_walks < 0xffffffffll && P.walk_length < 65536 && g_tuning.n2v_idx.load() != 1 &&
          g_tuning.n2v_rev.load() != 0;
 }
 
+bool pool_applies(const Node2vecParams& P, int member) {
+  return pool_possible(P, member) && (g_tuning.n2v_pool.load() == 2 || rev_pays(P));
+}
+
 // The triangle filter speaks about "x is a neighbour of t"; the walk asks "t is a neighbour of x": undirected
-// graphs only. With counters it runs only when the caller asked for this kernel's own counts.
+// graphs only. With the filter the pooled form wins wherever membership tests occur at all, i.e. whenever
+// prob_1 > prob_2 (q > 1): 6.26 against 7.16 ms for the per-lane kernel at (p, q) = (1, 2) on R-MAT 22, where the
+// unfiltered pooled kernel needs 7.89. With counters it runs only when the caller asked for this kernel's own counts.
 bool tri_applies(const Node2vecParams& P0, int member, bool sym) {
   if (!P0.colrev16 || !sym || P0.walk_length >= 32768 || g_tuning.n2v_tri.load() == 0) return false;
   Node2vecParams P = P0;
   if (P.counters) {
     if (g_tuning.n2v_count_kernel.load() != 1) return false;
-    P.counters = nullptr;  // pool_applies leaves instrumented launches to the per-lane kernel
+    P.counters = nullptr;  // the pooled kernels leave instrumented launches to the per-lane kernel
   }
-  return pool_applies(P, member);
+  return pool_possible(P, member) && (g_tuning.n2v_pool.load() == 2 || P.cut1 > P.cut2);
 }
 
 int launch_n2v(const Node2vecParams& P, bool sym, cudaStream_t s) {
