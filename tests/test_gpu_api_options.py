@@ -47,6 +47,22 @@ def test_reference_style_call_reaches_the_pooled_kernel_on_its_second_call(cuda,
     assert _lib.last_kernel() == "node2vec_walk_kernel"
 
 
+def test_trifilter_keyword(cuda, golden):
+    """trifilter=True on the operator builds the triangle filter with the graph (undirected graphs only)."""
+    g = golden
+    rowptr, col, start = _t(g["rowptr2"], cuda), _t(g["col2"], cuda), _t(g["start2"], cuda)
+    want = oracle.node2vec_walk(g["rowptr2"], g["col2"], g["start2"], 20, 0.25, 4.0, seed=3)
+    got = rejection_sampling(rowptr, col, start, 20, 0.25, 4.0, seed=3, symmetric=True, edgeset=True, trifilter=True)
+    assert _lib.last_kernel() == "node2vec_pool_tri_kernel"
+    np.testing.assert_array_equal(got.cpu().numpy(), want)
+    host = rejection_sampling(g["rowptr2"], g["col2"], g["start2"], 20, 0.25, 4.0, seed=3, symmetric=True, edgeset=True,
+                              trifilter=True)
+    assert _lib.last_kernel() == "node2vec_pool_tri_kernel"
+    np.testing.assert_array_equal(host.numpy(), want)
+    with pytest.raises(ValueError, match="symmetric"):
+        rejection_sampling(rowptr.clone(), col, start, 20, 0.25, 4.0, trifilter=True)
+
+
 def _shuffled_rows(rng, rowptr, col):
     col = col.copy()
     for v in range(rowptr.size - 1):
