@@ -102,6 +102,10 @@ class WalkGraph:
         # size of the edge hash set in 8-byte slots per edge: 2 = half full (the minimum), 4 = a quarter full;
         # None = the library's tuning (default 4), taken when the table fits half of the free device memory
         self.edgeset_slots_per_edge = None if edgeset_slots_per_edge is None else max(2.0, float(edgeset_slots_per_edge))
+        if trifilter and edgeset_slots_per_edge is None:
+            # behind the triangle filter few tests reach the hash set: a sparser table buys nothing there (88.1 against
+            # 88.2 ms on the headline workload) and costs its memory
+            self.edgeset_slots_per_edge = 2.0
         self.rows_sorted = None   # None: not checked yet (see check_rows_sorted)
         self.n2v_calls = 0        # node2vec calls served: edgeset="auto" builds the hash set on the second
         self._version = (rowptr._version, col._version)
