@@ -15,6 +15,9 @@
 // descriptor. Exact: the filter only ever says "certainly not". Same Philox draws, same decisions, same
 // outputs as the other kernels.
 //
+// A kernel of its own rather than a template flag of node2vec_pool_kernel: that kernel's speed depends on its exact
+// code shape (see its header) and it remains the kernel for graphs without a filter, so it is left untouched.
+//
 // Requires what node2vec_pool_kernel requires, a graph the caller declares undirected (WALK_B200_CSR_SYMMETRIC),
 // the records from walk_b200_trifilter_build, and walk_length < 32768.
 #pragma once
