@@ -197,3 +197,26 @@ def test_philox_restatement_matches_reference_statistics(golden, pq):
     wrong = [oracle.node2vec_walk(rowptr, col, start, 20, *other, seed=2000 + k) for k in range(runs)]
     _, _, p_wrong, _ = _stats.two_sample_chi2(_stats.triple_counts(np.concatenate(wrong), 2708), cb)
     assert p_wrong < 1e-6
+
+
+def test_attempt_cap_of_the_restatement_only_bites_when_it_runs_out(golden):
+    """max_attempts = 0 is the reference's unbounded loop; a cap no step reaches changes nothing; a small cap turns
+    exactly the steps that exhaust it into stand-still steps (edge id -1) and leaves the rows before them alone."""
+    g = golden
+    args = (g["rowptr2"], g["col2"], g["start2"], 20, 0.25, 4.0)
+    n0, e0, c0 = oracle.node2vec_walk(*args, seed=5, return_edges=True, return_counters=True)
+    n1, e1, c1 = oracle.node2vec_walk(*args, seed=5, return_edges=True, return_counters=True, max_attempts=1 << 22)
+    np.testing.assert_array_equal(n0, n1)
+    np.testing.assert_array_equal(e0, e1)
+    assert c0["steps_capped"] == 0 and c1["steps_capped"] == 0
+    n2, e2, c2 = oracle.node2vec_walk(*args, seed=5, return_edges=True, return_counters=True, max_attempts=2)
+    assert c2["steps_capped"] > 0
+    deg = np.diff(g["rowptr2"])
+    capped = (e2 == -1) & (deg[n2[:, :-1]] > 0)
+    assert capped.sum() == c2["steps_capped"]
+    assert (n2[:, 1:][capped] == n2[:, :-1][capped]).all()
+    # up to its first capped step a walk is the uncapped walk (same draws, same decisions)
+    first = np.where(capped.any(axis=1), capped.argmax(axis=1), 20)
+    for w in range(0, n2.shape[0], 37):
+        k = first[w]
+        np.testing.assert_array_equal(n2[w, :k + 1], n0[w, :k + 1])
