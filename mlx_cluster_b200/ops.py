@@ -106,6 +106,7 @@ class WalkGraph:
             # behind the triangle filter few tests reach the hash set: a sparser table buys nothing there (88.1 against
             # 88.2 ms on the headline workload) and costs its memory
             self.edgeset_slots_per_edge = 2.0
+        self.filter_declined = False  # edgeset="auto" looked at this graph for a triangle filter and left it
         self.rows_sorted = None   # None: not checked yet (see check_rows_sorted)
         self.n2v_calls = 0        # node2vec calls served: edgeset="auto" builds the hash set on the second
         self._version = (rowptr._version, col._version)
@@ -549,7 +550,7 @@ def random_walk(rowptr, col, start, rand, walk_length, *, stream=None, return_ed
     return _finish(g, out, e_out, check, return_edges, stream)
 
 
-def _membership_ready(g: WalkGraph, edgeset, stream, allow_auto: bool = True) -> None:
+def _membership_ready(g: WalkGraph, edgeset, stream, allow_auto: bool = True, q: float = 1.0) -> None:
     """Bring a graph into a state the node2vec kernels answer exactly on.
 
     ``edgeset=True`` builds the edge hash set now, ``False`` never does, ``"auto"`` (the default of
@@ -559,8 +560,14 @@ def _membership_ready(g: WalkGraph, edgeset, stream, allow_auto: bool = True) ->
     walked only once runs the binary-search kernel and allocates nothing). Without a hash set the membership
     test is a binary search over ``col``, which needs every row sorted; the reference's linear scan does not
     (``random_walks/BiasedRandomWalk.cpp:20-28``). So the rows are checked once per graph, and an unsorted
-    CSR gets the hash set (exact for any CSR) regardless -- or, with ``edgeset=False``, is refused."""
-    if g.edgeset is not None or g.num_edges == 0:
+    CSR gets the hash set (exact for any CSR) regardless -- or, with ``edgeset=False``, is refused.
+    A graph that keeps being walked (``_FILTER_AFTER_CALLS`` node2vec calls) with membership tests in play
+    (``q > 1``) and that turns out to be undirected -- every edge has its reverse, read off the reverse positions
+    in one pass -- also gets the triangle filter, if the device has room for 16 more bytes per edge."""
+    if g.num_edges == 0:
+        return
+    if g.edgeset is not None:
+        _maybe_filter(g, edgeset, stream, allow_auto, q)
         return
     if edgeset is True:
         g.build_edgeset(stream=stream)
@@ -573,6 +580,31 @@ def _membership_ready(g: WalkGraph, edgeset, stream, allow_auto: bool = True) ->
         return
     if allow_auto and edgeset == "auto" and g.n2v_calls >= 1 and g.num_nodes < 2**32 - 1 and g.edgeset_fits():
         g.build_edgeset(stream=stream)
+
+
+_FILTER_AFTER_CALLS = 16  # the filter takes about 20 launches' time to build and saves a fifth of every launch after
+
+
+def _maybe_filter(g: WalkGraph, edgeset, stream, allow_auto: bool, q: float) -> None:
+    if not (allow_auto and edgeset == "auto") or g.colrev16 is not None or g.colrev is None:
+        return
+    if g.n2v_calls < _FILTER_AFTER_CALLS or not q > 1.0 or g.filter_declined:
+        return
+    free, _ = torch.cuda.mem_get_info(g.device)
+    cached = torch.cuda.memory_reserved(g.device) - torch.cuda.memory_allocated(g.device)
+    if not g.symmetric:
+        # undirected <=> no edge lacks its reverse (reverse position 0xffffffff in the upper half of colrev)
+        with torch.cuda.device(g.device):
+            _sync_stream(stream, g.device)
+            undirected = not bool(((g.colrev >> 32) & 0xffffffff).eq(0xffffffff).any().item())
+        if not undirected:
+            g.filter_declined = True
+            return
+        g.symmetric = True
+    if 16 * g.num_edges * 1.2 + (256 << 20) > free + cached:
+        g.filter_declined = True
+        return
+    g.build_trifilter(stream=stream)
 
 
 def rejection_sampling(rowptr, col, start, walk_length, p, q, *, stream=None, seed: int = 0,
@@ -595,7 +627,8 @@ def rejection_sampling(rowptr, col, start, walk_length, p, q, *, stream=None, se
     hash set that answers with about one 32-byte read, for any CSR; ``False`` keeps the binary search
     over ``col`` (rows must be sorted: checked once per graph, an unsorted CSR raises); ``"auto"``
     (default) walks a graph's first call with the binary search and builds the hash set on its second
-    call if the device has room, and always builds it for a CSR whose rows are not sorted (a prepared
+    call if the device has room (and, from its 17th call on, the triangle filter if the graph proves to be
+    undirected and ``q > 1``), and always builds it for a CSR whose rows are not sorted (a prepared
     ``graph=`` is only checked for sorted rows and otherwise walked with the structures it has). None of
     this changes a result. ``trifilter=True`` (with ``symmetric=True``: undirected graphs only) also builds the
     triangle filter -- seconds per graph, after which a walk at p=0.25, q=4 gathers about half as much; for
@@ -635,7 +668,7 @@ def rejection_sampling(rowptr, col, start, walk_length, p, q, *, stream=None, se
     if validate:
         g.validate(start, check_sorted=False, stream=stream)
     # a graph the caller prepared keeps the structures it was given, except that unsorted rows get the hash set
-    _membership_ready(g, edgeset, stream, allow_auto=graph is None)
+    _membership_ready(g, edgeset, stream, allow_auto=graph is None, q=q)
     g.n2v_calls += 1
     with torch.cuda.device(dev):
         if out is None:

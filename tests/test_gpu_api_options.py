@@ -47,6 +47,38 @@ def test_reference_style_call_reaches_the_pooled_kernel_on_its_second_call(cuda,
     assert _lib.last_kernel() == "node2vec_walk_kernel"
 
 
+def test_a_graph_that_keeps_being_walked_gets_the_filter(cuda, golden):
+    """edgeset="auto": binary search on the first call, hash set from the second, and from the 17th the triangle
+    filter -- the graph is undirected, which the library finds out by itself; a directed graph never gets it."""
+    from mlx_cluster_b200 import ops
+    g = golden
+    rowptr, col, start = _t(g["rowptr2"], cuda), _t(g["col2"], cuda), _t(g["start2"], cuda)
+    want = oracle.node2vec_walk(g["rowptr2"], g["col2"], g["start2"], 20, 0.25, 4.0, seed=0)
+    seen = []
+    for call in range(ops._FILTER_AFTER_CALLS + 2):
+        got = rejection_sampling(rowptr, col, start, 20, 0.25, 4.0)
+        seen.append(_lib.last_kernel())
+        np.testing.assert_array_equal(got.cpu().numpy(), want)
+    assert seen[0] == "node2vec_walk_kernel" and seen[1] == "node2vec_pool_kernel"
+    assert seen[ops._FILTER_AFTER_CALLS - 1] == "node2vec_pool_kernel"
+    assert seen[ops._FILTER_AFTER_CALLS] == "node2vec_pool_tri_kernel" and seen[-1] == "node2vec_pool_tri_kernel"
+    # q <= 1: no membership test can matter, the filter is never built
+    rp2 = rowptr.clone()
+    for _ in range(ops._FILTER_AFTER_CALLS + 2):
+        rejection_sampling(rp2, col, start, 20, 1.0, 0.5)
+        assert _lib.last_kernel() != "node2vec_pool_tri_kernel"
+    # a directed graph (edges without a reverse) is recognised and left alone
+    rng = np.random.default_rng(4)
+    rp_d, cl_d = random_csr(rng, 300, 6.0, symmetric=False)
+    st_d = rng.integers(0, 300, 1500).astype(np.int64)
+    want_d = oracle.node2vec_walk(rp_d, cl_d, st_d, 12, 0.25, 4.0, seed=0)
+    rp_t, cl_t, st_t = _t(rp_d, cuda), _t(cl_d, cuda), _t(st_d, cuda)
+    for _ in range(ops._FILTER_AFTER_CALLS + 2):
+        got = rejection_sampling(rp_t, cl_t, st_t, 12, 0.25, 4.0)
+        assert _lib.last_kernel() != "node2vec_pool_tri_kernel"
+    np.testing.assert_array_equal(got.cpu().numpy(), want_d)
+
+
 def test_trifilter_keyword(cuda, golden):
     """trifilter=True on the operator builds the triangle filter with the graph (undirected graphs only)."""
     g = golden
