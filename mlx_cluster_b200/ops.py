@@ -596,7 +596,12 @@ def _maybe_filter(g: WalkGraph, edgeset, stream, allow_auto: bool, q: float) -> 
         # undirected <=> no edge lacks its reverse (reverse position 0xffffffff in the upper half of colrev)
         with torch.cuda.device(g.device):
             _sync_stream(stream, g.device)
-            undirected = not bool(((g.colrev >> 32) & 0xffffffff).eq(0xffffffff).any().item())
+            undirected = True
+            for c0 in range(0, g.num_edges, 1 << 26):  # in slices: the temporaries of one pass would double the graph
+                part = g.colrev[c0:c0 + (1 << 26)]
+                if bool(((part >> 32) & 0xffffffff).eq(0xffffffff).any().item()):
+                    undirected = False
+                    break
         if not undirected:
             g.filter_declined = True
             return
